@@ -1,0 +1,352 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path:  python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+One "step" is one pass of the hot path over one resident batch: the bf16 GEMM
+C[m,n] = A[m,k] B[n,k]^T at m=n=k=8192 (the shape the headline metric is quoted on).
+At N > 1 (launched by torchrun, one process per GPU) every rank holds A and its own
+8192-column block of B and computes its own column block of C — the column-sharded
+layout, weak scaling, no data-path collective.
+
+Prints ONE JSON line (rank 0):
+  value      whole-job TFLOP/s, inputs resident in HBM, CUDA-event timed, max over ranks
+  e2e        the same metric through the torch operator with HOST buffers: pinned-host -> device
+             copies of A and B and the device -> host copy of C inside the timed region
+  roofline   the GEMM kernel against the measured cuBLAS bf16 peak (MEASURED_PEAKS.json)
+  cpu_baseline  the oracle's CPU form (torch fp32 matmul on the host cores) on a bounded row band
+  plus comparators measured in the same process: cuBLAS (torch.matmul), the reference project's
+  own mma.sync kernel compiled for sm_100a (oracle/_ref, if built), and the RMSNorm kernels' GB/s.
+
+--impl reference times the reference path's CPU form (the reference has no CPU code of its
+own; its formula restated as torch fp32 matmul) on the host cores, rank 0 only.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+if REPO not in sys.path:
+    sys.path.insert(0, REPO)
+
+M = N = K = 8192
+WORKLOAD = "bf16 GEMM m=n=k=8192 TN (A[m,k] row-major, B[n,k]), U[-1,1] seed 1 (BASELINE configs[1])"
+METRIC = "hgemm_bf16_tflops_8192"
+UNIT = "TFLOP/s"
+
+
+def measured_peaks() -> dict:
+    path = os.path.join(REPO, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        d["_source"] = "measured"
+        return d
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "_source": "fallback"}
+
+
+def ncu_traffic(kernel_key: str):
+    """Per-launch DRAM bytes of a kernel from the committed ncu summary (profiles/traffic.json), or None."""
+    path = os.path.join(REPO, "profiles", "traffic.json")
+    if not os.path.exists(path):
+        return None
+    with open(path) as f:
+        return json.load(f).get(kernel_key)
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i", str(self.index),
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 7:
+                self.rows.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.thread.join(timeout=2)
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_gemm_baseline(target_seconds: float = 12.0) -> dict:
+    """torch CPU fp32 matmul on a row band of the 8192^3 problem (A band [rows, k] x full B)."""
+    import torch
+
+    torch.manual_seed(1)
+    b = (torch.rand(N, K) * 2 - 1).to(torch.bfloat16).float()
+    rows = 256
+    a = (torch.rand(rows, K) * 2 - 1).to(torch.bfloat16)
+    t0 = time.perf_counter()
+    torch.nn.functional.linear(a.float(), b)
+    dt = time.perf_counter() - t0
+    # grow the band towards the time target, bounded by the full problem
+    rows2 = int(min(M, max(rows, rows * target_seconds / max(dt, 1e-3) / 3)))
+    rows2 = max(256, rows2 // 256 * 256)
+    a = (torch.rand(rows2, K) * 2 - 1).to(torch.bfloat16)
+    best = None
+    for _ in range(3):
+        t0 = time.perf_counter()
+        torch.nn.functional.linear(a.float(), b)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    tflops = 2.0 * rows2 * N * K / best / 1e12
+    return {"value": tflops, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"torch CPU fp32 F.linear on a {rows2}-row band of A against all of B[{N},{K}] "
+                      f"(best of 3, {best * 1e3:.1f} ms; widening B to fp32 not timed)",
+            "host_cpus": os.cpu_count()}
+
+
+def run_reference_arm(args) -> None:
+    """The reference path's CPU form on the host cores; rank 0 only."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+
+    torch.manual_seed(1)
+    b = (torch.rand(N, K) * 2 - 1).to(torch.bfloat16).float()
+    rows = 1024
+    a = (torch.rand(rows, K) * 2 - 1).to(torch.bfloat16)
+    for _ in range(max(args.warmup, 1)):
+        torch.nn.functional.linear(a.float(), b)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        torch.nn.functional.linear(a.float(), b)
+    dt = time.perf_counter() - t0
+    tflops = 2.0 * rows * N * K * args.steps / dt / 1e12
+    cb = {"value": tflops, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+          "sample": f"each step = torch CPU fp32 F.linear of a {rows}-row band of A against all of B[{N},{K}]"}
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": tflops, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "note": "the reference has no CPU implementation; this is its oracle "
+                   "formula (src/impl/sgemm_impl.h:17-25) as an fp32 CPU matmul on a bounded row band"},
+        "cpu_baseline": cb,
+        "e2e": {"value": tflops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def time_cuda(fn, steps: int, warmup: int):
+    """ms per call: CUDA events on the current stream around `steps` back-to-back calls."""
+    import torch
+
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def rmsnorm_numbers(peaks: dict, steps: int, warmup: int) -> dict:
+    """RMSNorm fwd/bwd achieved GB/s at [32768, H] bf16 (algorithmic bytes 4RH+4H and 6RH+8H)."""
+    import torch
+
+    from peakgemm_b200 import capi
+
+    out = {}
+    R = 32768
+    for H in (4096, 8192):
+        g = torch.Generator(device="cuda").manual_seed(3)
+        x = torch.randn(R, H, device="cuda", generator=g).to(torch.bfloat16)
+        dy = torch.randn(R, H, device="cuda", generator=g).to(torch.bfloat16)
+        gamma = (1 + 0.1 * torch.randn(H, device="cuda", generator=g)).float()
+        y, dx, dg = torch.empty_like(x), torch.empty_like(x), torch.empty_like(gamma)
+        ws = torch.empty(capi.rmsnorm_bwd_workspace_bytes(R, H) // 4, device="cuda")
+        # x (+dy) and the outputs are 0.5-1.6 GB per call: far larger than the 126 MB L2
+        t_f = time_cuda(lambda: capi.rmsnorm_fwd(y, x, gamma), steps, warmup)
+        t_b = time_cuda(lambda: capi.rmsnorm_bwd(dx, dg, dy, x, gamma, ws), steps, warmup)
+        bf, bb = 4 * R * H + 4 * H, 6 * R * H + 8 * H
+        out[f"h{H}"] = {
+            "fwd_ms": t_f, "fwd_gbs": bf / t_f / 1e6, "fwd_frac_of_measured_hbm": bf / t_f / 1e6 / peaks["hbm_gbs"],
+            "bwd_ms": t_b, "bwd_gbs": bb / t_b / 1e6, "bwd_frac_of_measured_hbm": bb / t_b / 1e6 / peaks["hbm_gbs"],
+        }
+        del x, dy, y, dx
+    return out
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--variant", type=int, default=0, help="GEMM kernel variant (0 auto, 1 one-CTA, 2 CTA pair)")
+    ap.add_argument("--block-n", type=int, default=0)
+    ap.add_argument("--no-extras", action="store_true", help="skip comparators, RMSNorm, e2e and CPU legs")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import peakgemm_b200
+    from peakgemm_b200 import capi
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device: there is no CPU path"
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    peaks = measured_peaks()
+
+    # Inputs: generated on the device from seed 1 (the parity tests use CPU-generated copies of the
+    # same distribution); rank r holds A and the r-th 8192-column block of B.
+    g = torch.Generator(device="cuda").manual_seed(1)
+    a = (torch.rand(M, K, device="cuda", generator=g) * 2 - 1).to(torch.bfloat16)
+    g.manual_seed(1000 + rank)
+    b = (torch.rand(N, K, device="cuda", generator=g) * 2 - 1).to(torch.bfloat16)
+    c = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+
+    def step():
+        capi.hgemm(c, a, b, variant=args.variant, block_n=args.block_n)
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        if args.steps * 1.0 < 400:          # keep the sampler alive long enough for a few samples
+            t_end = time.time() + 0.5
+            while time.time() < t_end:
+                step()
+            torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    total_ms = ms.item()
+    ms_per_step = total_ms / args.steps
+    flops_step = 2.0 * M * N * K
+    value = world * flops_step / (ms_per_step * 1e-3) / 1e12
+    assert capi.device_status() == 0, "a GEMM kernel abandoned a bounded wait"
+
+    per_gpu = value / world
+    peak_key = "bf16_tflops" if total_ms < 1000 else "bf16_tflops_sustained"
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD if world == 1 else WORKLOAD + f"; x{world} ranks, rank r owns column block r "
+                   f"of B[{N * world},{K}] (A replicated), no gather", "l2": "inputs+output 403 MB per step > 126 MB L2",
+                   "kernel": f"variant={args.variant} block_n={args.block_n} (0 = automatic)"},
+        "gpu_launches": args.steps,
+        "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks[peak_key], "unit": "TFLOP/s",
+                     "frac": per_gpu / peaks[peak_key],
+                     "peak_source": f"{peaks['_source']} cuBLAS bf16 8192^3 ({peak_key})",
+                     "frac_of_nominal_2250": per_gpu / 2250.0,
+                     "traffic": ncu_traffic("hgemm_tcgen05_kernel_8192")},
+    }
+
+    if rank == 0 and not args.no_extras and world == 1:
+        # ---- end to end through the torch operator with host buffers
+        import PeakGemm
+
+        ah, bh = a.cpu().pin_memory(), b.cpu().pin_memory()
+        ch = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+        ad, bd, cd = torch.empty_like(a), torch.empty_like(b), torch.empty_like(c)
+
+        def e2e_step():
+            ad.copy_(ah, non_blocking=True)
+            bd.copy_(bh, non_blocking=True)
+            PeakGemm.gemm_peak(cd, ad, bd)
+            ch.copy_(cd, non_blocking=True)
+
+        e2e_steps = min(args.steps, 10)
+        t_e2e = time_cuda(e2e_step, e2e_steps, 3)
+        line["e2e"] = {"value": flops_step / (t_e2e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": t_e2e,
+                       "steps": e2e_steps, "h2d_bytes_per_step": 2 * (M * K + N * K),
+                       "d2h_bytes_per_step": 2 * M * N}
+        del ah, bh, ch, ad, bd, cd
+        # ---- comparators on the same GPU and inputs (never on the product path)
+        t_cublas = time_cuda(lambda: torch.matmul(a, b.t(), out=c), args.steps, args.warmup)
+        line["cublas"] = {"tflops": flops_step / (t_cublas * 1e-3) / 1e12, "ms": t_cublas}
+        ref_path = os.path.join(REPO, "oracle", "_ref", "libref_peakgemm.so")
+        if os.path.exists(ref_path):
+            ref = ctypes.CDLL(ref_path)
+            ref.ref_hgemm_peak.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_uint] * 3 + [ctypes.c_int, ctypes.c_void_p]
+            s = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+            t_ref = time_cuda(lambda: ref.ref_hgemm_peak(c.data_ptr(), a.data_ptr(), b.data_ptr(), M, N, K, 1, s),
+                              min(args.steps, 10), 3)
+            line["reference_kernel_on_this_gpu"] = {"tflops": flops_step / (t_ref * 1e-3) / 1e12, "ms": t_ref,
+                                                    "what": "reference mma.sync hgemm_peak compiled for sm_100a"}
+        line["rmsnorm"] = rmsnorm_numbers(peaks, args.steps, args.warmup)
+        line["cpu_baseline"] = cpu_gemm_baseline()
+    elif rank == 0 and world > 1:
+        line["e2e"] = None
+    line["clocks"] = clocks.summary()
+
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

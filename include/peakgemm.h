@@ -1,0 +1,136 @@
+/*
+ * peakgemm.h — C ABI of libPeakGemm_device.so (B200 / sm_100a only).
+ *
+ * Torch-free.  Every pointer is a DEVICE pointer on the device that is current
+ * when the call is made; every call is asynchronous on `stream` (a cudaStream_t
+ * passed as void*; NULL = the legacy default stream) and returns a pg_status.
+ * No call synchronises the device, and none allocates device memory except
+ * where a comment says so.
+ *
+ * The interface it replaces in the reference project (xytpai/PeakGemm) is the
+ * header-only launcher
+ *     hgemm::hgemm_peak(short* c, const short* a, const short* b,
+ *                       uint32 m, uint32 n, uint32 k, bool is_bf16, stream)
+ *         src/impl/hgemm_wmma_impl.h:412-423
+ * that src/ops/gemm.cpp:14-33 calls from the `gemm_peak` torch operator
+ * (src/register.cpp:4-7).
+ */
+#ifndef PEAKGEMM_H_
+#define PEAKGEMM_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Element types of A, B, C (GEMM) and x, y, dy, dx (RMSNorm). */
+enum pg_dtype { PG_F16 = 0, PG_BF16 = 1 };
+
+enum pg_status {
+    PG_OK = 0,
+    PG_ERR_BAD_ARG = 1,        /* null pointer, negative size, unknown dtype           */
+    PG_ERR_MISALIGNED = 2,     /* a base pointer is not 16-byte aligned                */
+    PG_ERR_UNSUPPORTED = 3,    /* n%8, k%8, ld%8 or H%8 violated, or size over a limit */
+    PG_ERR_WORKSPACE = 4,      /* caller's workspace is too small                      */
+    PG_ERR_CUDA = 5,           /* a CUDA runtime/driver call failed (see pg_last_cuda_error) */
+    PG_ERR_DEVICE_TIMEOUT = 6, /* a kernel gave up on a bounded wait (see pg_device_status)  */
+    PG_ERR_NOT_SM100 = 7       /* the current device is not compute capability 10.x    */
+};
+
+/* Human-readable name of a pg_status value; never NULL. */
+const char *pg_status_string(int status);
+
+/* cudaError_t (as int) of the last failing CUDA call made by this library on the
+ * calling thread, 0 if none. */
+int pg_last_cuda_error(void);
+
+/* Library version, "major.minor". */
+const char *pg_version(void);
+
+/*
+ * C[m,n] = A[m,k] * B[n,k]^T  (the reference's "TN" problem: A row-major,
+ * B stored [n,k] i.e. column-major [k,n]); products of the 16-bit inputs are
+ * accumulated in fp32 and rounded to nearest-even into C's 16-bit type; C is
+ * overwritten (no alpha/beta).
+ *
+ * Replaces hgemm::hgemm_peak (src/impl/hgemm_wmma_impl.h:412-423), with three
+ * additions: explicit row pitches lda/ldb/ldc in ELEMENTS (pass k, k, n for the
+ * reference's dense layout; ldc > n lets a column-sharded caller write its block
+ * straight into a full-width C), 64-bit sizes, and a status code in place of the
+ * reference's host assert (hgemm_wmma_impl.h:389-390).
+ *
+ * Preconditions (same as the reference's): n % 8 == 0, k % 8 == 0; additionally
+ * lda, ldb, ldc % 8 == 0 and 16-byte aligned base pointers.  m, n, k may be any
+ * size otherwise (row/column/k tails are handled; the reference reads out of
+ * bounds for m or n not a multiple of 128).  m == 0 or n == 0 is a no-op; k == 0
+ * zero-fills C.
+ *
+ * The kernel is a persistent, warp-specialised TMA + tcgen05 kernel with fp32
+ * accumulators in tensor memory.  It uses no scratch memory.
+ */
+int pg_hgemm(void *c, const void *a, const void *b,
+             int64_t m, int64_t n, int64_t k,
+             int64_t lda, int64_t ldb, int64_t ldc,
+             int dtype, void *stream);
+
+/*
+ * Same contract as pg_hgemm, with the kernel variant chosen by the caller:
+ *   variant 0 = automatic (what pg_hgemm uses)
+ *   variant 1 = one CTA per 128 x block_n tile   (tcgen05 cta_group::1)
+ *   variant 2 = CTA pair per 256 x block_n tile  (tcgen05 cta_group::2)
+ *   block_n   = 0 (automatic), 64, 128 or 256
+ * Meant for benchmarks and tests; the reference fixes one configuration at
+ * compile time (REGISTER_HGEMM_WMMA_M16N8K16_IMPL, hgemm_wmma_impl.h:410).
+ */
+int pg_hgemm_ex(void *c, const void *a, const void *b,
+                int64_t m, int64_t n, int64_t k,
+                int64_t lda, int64_t ldb, int64_t ldc,
+                int dtype, int variant, int block_n, void *stream);
+
+/*
+ * Device-side status word of the GEMM kernels on the current device: 0 if no
+ * kernel has given up on a bounded wait since the last call, otherwise a code
+ * that names the waiting role.  Synchronises `stream`, reads the word, clears
+ * it.  Returns PG_OK and writes *device_status, or an error status.
+ */
+int pg_device_status(int *device_status, void *stream);
+
+/*
+ * RMSNorm forward over `rows` rows of length h:
+ *     rstd_r = rsqrt(mean_j(x[r,j]^2) + eps)
+ *     y[r,j] = round_to_dtype((x[r,j] * rstd_r) * gamma[j])
+ * x, y: [rows, h] of `dtype`, dense row-major; gamma: [h] fp32.  All arithmetic
+ * in fp32.  Requires h % 8 == 0.  Uses no scratch memory.
+ *
+ * The reference project has no RMSNorm operator; this entry point follows the
+ * conventions of its GEMM launcher (outputs first, caller-allocated buffers,
+ * asynchronous on the given stream).
+ */
+int pg_rmsnorm_fwd(void *y, const void *x, const float *gamma,
+                   int64_t rows, int64_t h, float eps, int dtype, void *stream);
+
+/* Bytes of scratch pg_rmsnorm_bwd needs for this shape on the current device. */
+size_t pg_rmsnorm_bwd_workspace_bytes(int64_t rows, int64_t h);
+
+/*
+ * RMSNorm backward.  With xhat = x * rstd and g = dy * gamma (fp32):
+ *     dx[r,j]   = round_to_dtype(rstd_r * (g[r,j] - xhat[r,j] * mean_j(g[r,:] * xhat[r,:])))
+ *     dgamma[j] = sum_r dy[r,j] * xhat[r,j]                       (fp32, overwritten)
+ * rstd is recomputed from x, so no saved state crosses the interface.
+ * dy, x, dx: [rows, h] of `dtype`; gamma, dgamma: [h] fp32.  Requires h % 8 == 0.
+ *
+ * dgamma is reduced in two passes and is deterministic: every CTA writes one
+ * fp32 partial row into `workspace` ([n_cta, h] fp32, at least
+ * pg_rmsnorm_bwd_workspace_bytes bytes, 16-byte aligned), then a second kernel
+ * sums the partial rows in a fixed order.  The workspace needs no initialisation.
+ */
+int pg_rmsnorm_bwd(void *dx, float *dgamma, const void *dy, const void *x,
+                   const float *gamma, int64_t rows, int64_t h, float eps,
+                   int dtype, void *workspace, size_t workspace_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PEAKGEMM_H_ */

@@ -1,0 +1,166 @@
+"""TEST INFRASTRUCTURE — the correctness oracle.  Not part of the product.
+
+Only tests/, __graft_entry__.smoke() and the CPU-baseline legs of bench.py may
+import this package; nothing under peakgemm_b200/ does.
+
+GEMM oracle: the reference project checks its half-precision kernel against
+``sgemm::sgemm_naive_kernel`` (src/impl/sgemm_impl.h:9-26; used by
+test/cpp/test_gemm_half.cpp:62-63): ``acc_fp32 += float(a[mi*k+ki]) * float(b[ni*k+ki])``
+over increasing ki, then a cast to the 16-bit type.  ``gemm_exact`` is that loop
+in C (oracle/gemm_oracle.c, bit-identical to the reference kernel because the
+products are exact in fp32); ``gemm_fp32`` is the same contraction through
+torch's CPU fp32 matmul (summation order differs; what test/test_gemm.py:37-38
+does with F.linear) and is the fast form used for large shapes and as the timed
+CPU baseline.
+
+PARITY PINNING.  The reference ships no golden vectors for this path (its tests
+use unseeded random inputs and print, test/cpp/test_gemm_half.cpp:37-46,
+test/test_gemm.py:55-60).  The GEMM oracle is pinned against outputs of the
+reference's own kernels run on a B200 (tests/golden/, made by
+tests/golden/make_golden.py from oracle/_ref/libref_peakgemm.so).
+
+RMSNorm oracle: PARITY UNPINNED — the reference has no RMSNorm operator, kernel or
+test.  The oracle is the textbook definition in fp32 (what
+torch.nn.functional.rms_norm computes) with the closed-form gradients.
+"""
+from __future__ import annotations
+
+import ctypes
+import importlib.util
+import math
+import os
+
+import numpy as np
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _builder():
+    spec = importlib.util.spec_from_file_location("_oracle_build", os.path.join(_HERE, "build_oracle.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+_cpu_lib = None
+
+
+def cpu_lib() -> ctypes.CDLL:
+    global _cpu_lib
+    if _cpu_lib is None:
+        path = _builder().build_cpu()
+        lib = ctypes.CDLL(path)
+        i64, p = ctypes.c_int64, ctypes.c_void_p
+        for name in ("oracle_gemm", "oracle_gemm_acc"):
+            fn = getattr(lib, name)
+            fn.restype = ctypes.c_int
+            fn.argtypes = [p, p, p, i64, i64, i64, ctypes.c_int]
+        _cpu_lib = lib
+    return _cpu_lib
+
+
+def _bits(t: torch.Tensor) -> np.ndarray:
+    assert t.dtype in (torch.bfloat16, torch.float16) and t.device.type == "cpu"
+    return t.contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+def gemm_exact(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """C = A @ B^T exactly as sgemm_naive_kernel computes it (k-ordered fp32 sum, cast to a.dtype)."""
+    m, k = a.shape
+    n = b.shape[0]
+    assert b.shape[1] == k and a.dtype == b.dtype
+    ab, bb = _bits(a), _bits(b)
+    c = np.empty((m, n), dtype=np.uint16)
+    r = cpu_lib().oracle_gemm(c.ctypes.data, ab.ctypes.data, bb.ctypes.data, m, n, k, int(a.dtype == torch.bfloat16))
+    assert r == 0
+    return torch.from_numpy(c.view(np.int16)).view(a.dtype)
+
+
+def gemm_exact_acc(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """The unrounded fp32 accumulators of gemm_exact."""
+    m, k = a.shape
+    n = b.shape[0]
+    ab, bb = _bits(a), _bits(b)
+    acc = np.empty((m, n), dtype=np.float32)
+    r = cpu_lib().oracle_gemm_acc(acc.ctypes.data, ab.ctypes.data, bb.ctypes.data, m, n, k,
+                                  int(a.dtype == torch.bfloat16))
+    assert r == 0
+    return torch.from_numpy(acc)
+
+
+def gemm_fp32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """fp32 C = A.float() @ B.float()^T on the CPU (torch); unrounded."""
+    return torch.nn.functional.linear(a.float(), b.float())
+
+
+def gemm_tolerance(k: int, c_ref: torch.Tensor) -> float:
+    """Acceptance bound on max|C - C_ref| for 16-bit outputs: 2e-2 * sqrt(k/4096) * max|C_ref|."""
+    return 2e-2 * math.sqrt(max(k, 1) / 4096.0) * float(c_ref.abs().max())
+
+
+def reference_abs_tolerance(k: int) -> float:
+    """The reference test's own bound: |out - ref| <= 0.5 * k / 4096 (test_gemm_half.cpp:158,167)."""
+    return 0.5 * k / 4096.0
+
+
+# ------------------------------------------------------------------ RMSNorm ----
+
+def rmsnorm_fwd(x: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """fp32 y (unrounded) = x * rsqrt(mean(x^2) + eps) * gamma over the last dimension."""
+    xf = x.float()
+    rstd = torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + eps)
+    return (xf * rstd) * gamma.float()
+
+
+def rmsnorm_bwd(dy: torch.Tensor, x: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-6):
+    """fp32 (dx, dgamma), closed form:  dx = rstd * (g - xhat * mean(g * xhat)),  dgamma = sum_rows dy * xhat."""
+    xf, dyf, g32 = x.float(), dy.float(), gamma.float()
+    rstd = torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + eps)
+    xhat = xf * rstd
+    g = dyf * g32
+    dx = rstd * (g - xhat * (g * xhat).mean(dim=-1, keepdim=True))
+    dgamma = (dyf * xhat).reshape(-1, x.shape[-1]).double().sum(dim=0).float()
+    return dx, dgamma
+
+
+def ulp_distance_16(out: torch.Tensor, ref_fp32: torch.Tensor) -> torch.Tensor:
+    """|out - round(ref)| in units of out's 16-bit ulp at round(ref), elementwise (int64).
+
+    Both are mapped to a monotone integer line (sign-magnitude -> two's complement),
+    so the difference counts representable values between them."""
+    ref = ref_fp32.to(out.dtype)
+
+    def line(t):
+        i = t.contiguous().view(torch.int16).to(torch.int64)
+        return torch.where(i < 0, -(i & 0x7FFF), i)
+
+    return (line(out) - line(ref)).abs()
+
+
+# ------------------------------------------------------------ input generators ----
+# Seeded on the CPU so the oracle and the GPU see identical bits.
+
+def gemm_inputs_uniform(m: int, n: int, k: int, dtype: torch.dtype, seed: int):
+    """A[m,k], B[n,k] ~ U[-1,1] (the distribution of test/test_gemm.py:24-29), drawn A then B."""
+    g = torch.Generator().manual_seed(seed)
+    a = (torch.rand(m, k, generator=g) * 2 - 1).to(dtype)
+    b = (torch.rand(n, k, generator=g) * 2 - 1).to(dtype)
+    return a, b
+
+
+def gemm_inputs_llm(m: int, n: int, k: int, dtype: torch.dtype, seed: int):
+    """Activations A ~ N(0,1), weights B ~ N(0, 0.02)."""
+    g = torch.Generator().manual_seed(seed)
+    a = torch.randn(m, k, generator=g).to(dtype)
+    b = (0.02 * torch.randn(n, k, generator=g)).to(dtype)
+    return a, b
+
+
+def rmsnorm_inputs(rows: int, h: int, dtype: torch.dtype, seed: int):
+    """x, dy ~ N(0,1) in `dtype`; gamma ~ N(1, 0.1) fp32; drawn x, dy, gamma."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(rows, h, generator=g).to(dtype)
+    dy = torch.randn(rows, h, generator=g).to(dtype)
+    gamma = 1 + 0.1 * torch.randn(h, generator=g)
+    return x, dy, gamma

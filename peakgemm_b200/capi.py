@@ -1,0 +1,111 @@
+"""ctypes binding of the C ABI in include/peakgemm.h (libPeakGemm_device.so).
+
+This is the binding a non-torch host would write; the tests and the benchmark use
+it to call the device library exactly as the torch shim does, with raw device
+pointers.  Loading fails loudly if the library has not been built.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_this_dir = os.path.dirname(os.path.abspath(__file__))
+DEVICE_LIB_PATH = os.path.join(_this_dir, "libPeakGemm_device.so")
+
+PG_F16, PG_BF16 = 0, 1
+PG_OK = 0
+
+# name -> (restype, argtypes); every symbol include/peakgemm.h declares
+_p, _i64, _i, _f, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
+SIGNATURES = {
+    "pg_status_string": (ctypes.c_char_p, [_i]),
+    "pg_last_cuda_error": (_i, []),
+    "pg_version": (ctypes.c_char_p, []),
+    "pg_hgemm": (_i, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _p]),
+    "pg_hgemm_ex": (_i, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _p]),
+    "pg_device_status": (_i, [ctypes.POINTER(_i), _p]),
+    "pg_rmsnorm_fwd": (_i, [_p, _p, _p, _i64, _i64, _f, _i, _p]),
+    "pg_rmsnorm_bwd_workspace_bytes": (_sz, [_i64, _i64]),
+    "pg_rmsnorm_bwd": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _f, _i, _p, _sz, _p]),
+}
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(DEVICE_LIB_PATH):
+            raise ImportError(
+                f"{DEVICE_LIB_PATH} is not built; run `python peakgemm_b200/csrc/build.py`"
+            )
+        l = ctypes.CDLL(DEVICE_LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(l, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = l
+    return _lib
+
+
+class PeakGemmError(RuntimeError):
+    def __init__(self, status: int, where: str):
+        self.status = status
+        msg = lib().pg_status_string(status).decode()
+        super().__init__(f"{where}: {msg} (cuda error {lib().pg_last_cuda_error()})")
+
+
+def check(status: int, where: str) -> None:
+    if status != PG_OK:
+        raise PeakGemmError(status, where)
+
+
+def dtype_code(torch_dtype) -> int:
+    import torch
+
+    if torch_dtype == torch.float16:
+        return PG_F16
+    if torch_dtype == torch.bfloat16:
+        return PG_BF16
+    raise TypeError(f"unsupported dtype {torch_dtype}")
+
+
+def _stream_ptr(stream=None):
+    import torch
+
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return ctypes.c_void_p(s.cuda_stream)
+
+
+def hgemm(c, a, b, *, variant: int = 0, block_n: int = 0, ldc: int | None = None, stream=None) -> None:
+    """C[m,n] = A[m,k] @ B[n,k]^T through pg_hgemm_ex on torch CUDA tensors (2-D, row-major)."""
+    m, k = a.shape
+    n = b.shape[0]
+    st = lib().pg_hgemm_ex(c.data_ptr(), a.data_ptr(), b.data_ptr(), m, n, k, a.stride(0) if m > 1 else k,
+                           b.stride(0) if n > 1 else k, ldc if ldc is not None else (c.stride(0) if m > 1 else n),
+                           dtype_code(a.dtype), variant, block_n, _stream_ptr(stream))
+    check(st, "pg_hgemm_ex")
+
+
+def device_status(stream=None) -> int:
+    out = ctypes.c_int(0)
+    check(lib().pg_device_status(ctypes.byref(out), _stream_ptr(stream)), "pg_device_status")
+    return out.value
+
+
+def rmsnorm_fwd(y, x, gamma, eps: float = 1e-6, stream=None) -> None:
+    rows, h = x.shape
+    check(lib().pg_rmsnorm_fwd(y.data_ptr(), x.data_ptr(), gamma.data_ptr(), rows, h, eps,
+                               dtype_code(x.dtype), _stream_ptr(stream)), "pg_rmsnorm_fwd")
+
+
+def rmsnorm_bwd_workspace_bytes(rows: int, h: int) -> int:
+    return int(lib().pg_rmsnorm_bwd_workspace_bytes(rows, h))
+
+
+def rmsnorm_bwd(dx, dgamma, dy, x, gamma, workspace, eps: float = 1e-6, stream=None) -> None:
+    rows, h = x.shape
+    check(lib().pg_rmsnorm_bwd(dx.data_ptr(), dgamma.data_ptr(), dy.data_ptr(), x.data_ptr(), gamma.data_ptr(),
+                               rows, h, eps, dtype_code(x.dtype), workspace.data_ptr(),
+                               workspace.numel() * workspace.element_size(), _stream_ptr(stream)),
+          "pg_rmsnorm_bwd")

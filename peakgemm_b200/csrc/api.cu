@@ -1,0 +1,142 @@
+// The C ABI of libPeakGemm_device.so: argument checks, status codes, dispatch.
+// Declarations and contracts: include/peakgemm.h.
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/peakgemm.h"
+#include "gemm_sm100.h"
+#include "rmsnorm.h"
+
+namespace {
+
+thread_local int t_last_cuda_error = 0;
+
+int cuda_fail(cudaError_t e) {
+    t_last_cuda_error = static_cast<int>(e);
+    cudaGetLastError();   // clear the sticky-free error state of this thread
+    return PG_ERR_CUDA;
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int from_launch(int r, cudaError_t e) {
+    switch (r) {
+        case pg::kLaunchOk: return PG_OK;
+        case pg::kLaunchCuda: return cuda_fail(e);
+        case pg::kLaunchNotSm100: return PG_ERR_NOT_SM100;
+        default: return PG_ERR_BAD_ARG;
+    }
+}
+
+constexpr int64_t kMaxDim = (int64_t(1) << 31) - 1;
+
+}  // namespace
+
+extern "C" {
+
+const char *pg_status_string(int status) {
+    switch (status) {
+        case PG_OK: return "PG_OK";
+        case PG_ERR_BAD_ARG: return "PG_ERR_BAD_ARG: null pointer, negative size or unknown dtype/variant";
+        case PG_ERR_MISALIGNED: return "PG_ERR_MISALIGNED: base pointers must be 16-byte aligned";
+        case PG_ERR_UNSUPPORTED: return "PG_ERR_UNSUPPORTED: n, k, lda, ldb, ldc and h must be multiples of 8 and within limits";
+        case PG_ERR_WORKSPACE: return "PG_ERR_WORKSPACE: workspace too small";
+        case PG_ERR_CUDA: return "PG_ERR_CUDA: a CUDA call failed (pg_last_cuda_error)";
+        case PG_ERR_DEVICE_TIMEOUT: return "PG_ERR_DEVICE_TIMEOUT: a kernel abandoned a bounded wait";
+        case PG_ERR_NOT_SM100: return "PG_ERR_NOT_SM100: the current device is not compute capability 10.x";
+        default: return "unknown pg_status";
+    }
+}
+
+int pg_last_cuda_error(void) { return t_last_cuda_error; }
+
+const char *pg_version(void) { return "0.1"; }
+
+int pg_hgemm_ex(void *c, const void *a, const void *b, int64_t m, int64_t n, int64_t k, int64_t lda,
+                int64_t ldb, int64_t ldc, int dtype, int variant, int block_n, void *stream) {
+    if (m < 0 || n < 0 || k < 0) return PG_ERR_BAD_ARG;
+    if (dtype != PG_F16 && dtype != PG_BF16) return PG_ERR_BAD_ARG;
+    if (variant < 0 || variant > 2) return PG_ERR_BAD_ARG;
+    if (block_n != 0 && block_n != 64 && block_n != 128 && block_n != 256) return PG_ERR_BAD_ARG;
+    if (m == 0 || n == 0) return PG_OK;
+    if (!c || (k > 0 && (!a || !b))) return PG_ERR_BAD_ARG;
+    if (lda < k || ldb < k || ldc < n) return PG_ERR_BAD_ARG;
+    if (n % 8 != 0 || k % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0 || ldc % 8 != 0) return PG_ERR_UNSUPPORTED;
+    if (m > kMaxDim || n > kMaxDim || k > kMaxDim) return PG_ERR_UNSUPPORTED;
+    if (!aligned16(c) || (k > 0 && (!aligned16(a) || !aligned16(b)))) return PG_ERR_MISALIGNED;
+    pg::GemmArgs g{c, a, b, m, n, k, lda, ldb, ldc, dtype == PG_BF16};
+    cudaError_t e = cudaSuccess;
+    const int r = pg::hgemm_launch(g, variant, block_n, static_cast<cudaStream_t>(stream), &e);
+    return from_launch(r, e);
+}
+
+int pg_hgemm(void *c, const void *a, const void *b, int64_t m, int64_t n, int64_t k, int64_t lda,
+             int64_t ldb, int64_t ldc, int dtype, void *stream) {
+    return pg_hgemm_ex(c, a, b, m, n, k, lda, ldb, ldc, dtype, 0, 0, stream);
+}
+
+int pg_device_status(int *device_status, void *stream) {
+    if (!device_status) return PG_ERR_BAD_ARG;
+    cudaError_t e = cudaSuccess;
+    const int r = pg::gemm_device_status(device_status, static_cast<cudaStream_t>(stream), &e);
+    return from_launch(r, e);
+}
+
+int pg_rmsnorm_fwd(void *y, const void *x, const float *gamma, int64_t rows, int64_t h, float eps,
+                   int dtype, void *stream) {
+    if (rows < 0 || h <= 0) return PG_ERR_BAD_ARG;
+    if (dtype != PG_F16 && dtype != PG_BF16) return PG_ERR_BAD_ARG;
+    if (rows == 0) return PG_OK;
+    if (!y || !x || !gamma) return PG_ERR_BAD_ARG;
+    if (h % 8 != 0 || h > kMaxDim) return PG_ERR_UNSUPPORTED;
+    if (!aligned16(y) || !aligned16(x) || !aligned16(gamma)) return PG_ERR_MISALIGNED;
+    pg::RmsFwdArgs a{y, x, gamma, rows, h, eps, dtype == PG_BF16};
+    const cudaError_t e = pg::rmsnorm_fwd_launch(a, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? PG_OK : cuda_fail(e);
+}
+
+size_t pg_rmsnorm_bwd_workspace_bytes(int64_t rows, int64_t h) {
+    if (rows <= 0 || h <= 0 || h % 8 != 0 || h > pg::rmsnorm_max_h()) return 0;
+    int ctas = 0;
+    // the CTA count does not depend on the element type; bf16 and fp16 kernels have the same footprint
+    if (pg::rmsnorm_bwd_ctas(rows, h, true, &ctas) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    int ctas16 = 0;
+    if (pg::rmsnorm_bwd_ctas(rows, h, false, &ctas16) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    if (ctas16 > ctas) ctas = ctas16;
+    return static_cast<size_t>(ctas) * static_cast<size_t>(h) * sizeof(float);
+}
+
+int pg_rmsnorm_bwd(void *dx, float *dgamma, const void *dy, const void *x, const float *gamma,
+                   int64_t rows, int64_t h, float eps, int dtype, void *workspace,
+                   size_t workspace_bytes, void *stream) {
+    if (rows < 0 || h <= 0) return PG_ERR_BAD_ARG;
+    if (dtype != PG_F16 && dtype != PG_BF16) return PG_ERR_BAD_ARG;
+    if (!dgamma) return PG_ERR_BAD_ARG;
+    if (h % 8 != 0 || h > pg::rmsnorm_max_h()) return PG_ERR_UNSUPPORTED;
+    if (!aligned16(dgamma)) return PG_ERR_MISALIGNED;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (rows == 0) {   // an empty sum
+        const cudaError_t e = cudaMemsetAsync(dgamma, 0, static_cast<size_t>(h) * sizeof(float), s);
+        return e == cudaSuccess ? PG_OK : cuda_fail(e);
+    }
+    if (!dx || !dy || !x || !gamma || !workspace) return PG_ERR_BAD_ARG;
+    if (!aligned16(dx) || !aligned16(dy) || !aligned16(x) || !aligned16(gamma) || !aligned16(workspace))
+        return PG_ERR_MISALIGNED;
+    int ctas = 0;
+    cudaError_t e = pg::rmsnorm_bwd_ctas(rows, h, dtype == PG_BF16, &ctas);
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (workspace_bytes < static_cast<size_t>(ctas) * static_cast<size_t>(h) * sizeof(float))
+        return PG_ERR_WORKSPACE;
+    pg::RmsBwdArgs a{dx, dgamma, dy, x, gamma, rows, h, eps, dtype == PG_BF16, workspace};
+    e = pg::rmsnorm_bwd_launch(a, ctas, s);
+    return e == cudaSuccess ? PG_OK : cuda_fail(e);
+}
+
+}  // extern "C"

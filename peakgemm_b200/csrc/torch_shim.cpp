@@ -1,0 +1,111 @@
+// libPeakGemm.so: the PyTorch operator surface over the C ABI (include/peakgemm.h).
+// Plain C++ (no CUDA code in this file), so it never needs nvcc.
+//
+// Mirrors the reference project's registration and host code:
+//   TORCH_LIBRARY(PeakGemm, m) with the schema string of src/register.cpp:4-7,
+//   gemm_peak(Tensor& c, Tensor& a, Tensor& b, int64 m, n, k) of src/ops/gemm.cpp:5-45:
+//   contiguity check, device guard on `a`, the current CUDA stream, dispatch on a's dtype,
+//   asynchronous launch, nothing returned, `c` written in place.
+// Differences, all on the error side: arguments the reference leaves unchecked
+// (device, dtype equality, shapes against m/n/k) raise c10::Error here instead of
+// reading out of bounds, and fp32/fp64 inputs are refused (the reference sends
+// fp32 to its unoptimised sgemm path, src/ops/gemm.cpp:34-43).
+//
+// rms_norm_fwd / rms_norm_bwd have no counterpart in the reference; they follow
+// the same conventions: outputs first, caller-allocated, in place, return ().
+
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/core/DeviceGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/library.h>
+
+#include "../../include/peakgemm.h"
+
+namespace {
+
+using at::Tensor;
+
+int dtype_code(const Tensor &t, const char *op) {
+    if (t.scalar_type() == at::kHalf) return PG_F16;
+    if (t.scalar_type() == at::kBFloat16) return PG_BF16;
+    TORCH_CHECK(false, op, ": only float16 and bfloat16 are built for sm_100a, got ", t.scalar_type());
+    return -1;
+}
+
+void check_status(int st, const char *op) {
+    TORCH_CHECK(st == PG_OK, op, ": ", pg_status_string(st),
+                st == PG_ERR_CUDA ? " cudaError=" : "", st == PG_ERR_CUDA ? std::to_string(pg_last_cuda_error()) : "");
+}
+
+void gemm_peak(Tensor &c, Tensor &a, Tensor &b, int64_t m, int64_t n, int64_t k) {
+    TORCH_CHECK(c.is_contiguous() && a.is_contiguous() && b.is_contiguous());
+    TORCH_CHECK(a.is_cuda() && b.is_cuda() && c.is_cuda(), "gemm_peak: tensors must be on a CUDA device");
+    TORCH_CHECK(a.device() == b.device() && a.device() == c.device(), "gemm_peak: tensors on different devices");
+    TORCH_CHECK(a.scalar_type() == b.scalar_type() && a.scalar_type() == c.scalar_type(),
+                "gemm_peak: a, b, c must have one dtype");
+    TORCH_CHECK(m >= 0 && n >= 0 && k >= 0 && a.numel() == m * k && b.numel() == n * k && c.numel() == m * n,
+                "gemm_peak: tensor sizes do not match m, n, k");
+    const int dt = dtype_code(a, "gemm_peak");
+    c10::DeviceGuard device_guard(a.device());
+    auto stream = at::cuda::getCurrentCUDAStream();
+    check_status(pg_hgemm(c.data_ptr(), a.data_ptr(), b.data_ptr(), m, n, k, k, k, n, dt, stream.stream()),
+                 "gemm_peak");
+}
+
+void rms_norm_fwd(Tensor &y, Tensor &x, Tensor &gamma, double eps) {
+    TORCH_CHECK(y.is_contiguous() && x.is_contiguous() && gamma.is_contiguous());
+    TORCH_CHECK(x.is_cuda() && y.is_cuda() && gamma.is_cuda(), "rms_norm_fwd: tensors must be on a CUDA device");
+    TORCH_CHECK(x.device() == y.device() && x.device() == gamma.device(), "rms_norm_fwd: tensors on different devices");
+    TORCH_CHECK(x.dim() >= 1 && x.sizes() == y.sizes() && x.scalar_type() == y.scalar_type(),
+                "rms_norm_fwd: y must have x's shape and dtype");
+    const int64_t h = x.size(-1);
+    TORCH_CHECK(gamma.scalar_type() == at::kFloat && gamma.numel() == h, "rms_norm_fwd: gamma must be float32 [h]");
+    const int64_t rows = h > 0 ? x.numel() / h : 0;
+    const int dt = dtype_code(x, "rms_norm_fwd");
+    c10::DeviceGuard device_guard(x.device());
+    auto stream = at::cuda::getCurrentCUDAStream();
+    check_status(pg_rmsnorm_fwd(y.data_ptr(), x.data_ptr(), gamma.data_ptr<float>(), rows, h,
+                                static_cast<float>(eps), dt, stream.stream()),
+                 "rms_norm_fwd");
+}
+
+void rms_norm_bwd(Tensor &dx, Tensor &dgamma, Tensor &dy, Tensor &x, Tensor &gamma, double eps) {
+    TORCH_CHECK(dx.is_contiguous() && dgamma.is_contiguous() && dy.is_contiguous() && x.is_contiguous() &&
+                gamma.is_contiguous());
+    TORCH_CHECK(x.is_cuda() && dx.is_cuda() && dy.is_cuda() && gamma.is_cuda() && dgamma.is_cuda(),
+                "rms_norm_bwd: tensors must be on a CUDA device");
+    TORCH_CHECK(x.device() == dx.device() && x.device() == dy.device() && x.device() == gamma.device() &&
+                    x.device() == dgamma.device(),
+                "rms_norm_bwd: tensors on different devices");
+    TORCH_CHECK(x.dim() >= 1 && x.sizes() == dx.sizes() && x.sizes() == dy.sizes() &&
+                    x.scalar_type() == dx.scalar_type() && x.scalar_type() == dy.scalar_type(),
+                "rms_norm_bwd: dx and dy must have x's shape and dtype");
+    const int64_t h = x.size(-1);
+    TORCH_CHECK(gamma.scalar_type() == at::kFloat && gamma.numel() == h && dgamma.scalar_type() == at::kFloat &&
+                    dgamma.numel() == h,
+                "rms_norm_bwd: gamma and dgamma must be float32 [h]");
+    const int64_t rows = h > 0 ? x.numel() / h : 0;
+    const int dt = dtype_code(x, "rms_norm_bwd");
+    c10::DeviceGuard device_guard(x.device());
+    auto stream = at::cuda::getCurrentCUDAStream();
+    // Scratch for the per-CTA dgamma partial rows comes from torch's caching
+    // allocator: stream-ordered, no cudaMalloc in steady state.
+    const size_t ws_bytes = pg_rmsnorm_bwd_workspace_bytes(rows, h);
+    Tensor ws = at::empty({static_cast<int64_t>(ws_bytes > 0 ? ws_bytes : 16)}, x.options().dtype(at::kByte));
+    check_status(pg_rmsnorm_bwd(dx.data_ptr(), dgamma.data_ptr<float>(), dy.data_ptr(), x.data_ptr(),
+                                gamma.data_ptr<float>(), rows, h, static_cast<float>(eps), dt, ws.data_ptr(),
+                                ws_bytes, stream.stream()),
+                 "rms_norm_bwd");
+}
+
+}  // namespace
+
+TORCH_LIBRARY(PeakGemm, m) {
+    m.def("gemm_peak(Tensor c, Tensor a, Tensor b, SymInt m, SymInt n, SymInt k) -> ()");
+    m.impl("gemm_peak", &gemm_peak);
+    m.def("rms_norm_fwd(Tensor y, Tensor x, Tensor gamma, float eps) -> ()");
+    m.impl("rms_norm_fwd", &rms_norm_fwd);
+    m.def("rms_norm_bwd(Tensor dx, Tensor dgamma, Tensor dy, Tensor x, Tensor gamma, float eps) -> ()");
+    m.impl("rms_norm_bwd", &rms_norm_bwd);
+}

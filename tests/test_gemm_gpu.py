@@ -1,0 +1,202 @@
+"""GPU parity of the tcgen05 GEMM with the oracle, called through the C ABI (pg_hgemm_ex).
+
+Bound for every case: max|C - C_ref| <= 2e-2 * sqrt(k/4096) * max|C_ref| (C_ref = fp32-accumulated
+product of the same 16-bit inputs), plus the reference test's own bound 0.5*k/4096 against the exact
+k-ordered oracle where that is affordable.  Inputs are generated on the CPU from fixed seeds, C is
+pre-filled with garbage (the reference's tests do the same: test/test_gemm.py:32-34).
+"""
+import pytest
+import torch
+
+import oracle
+from tests import helpers
+
+pytestmark = pytest.mark.gpu
+
+BF16, F16 = torch.bfloat16, torch.float16
+
+
+def run_case(m, n, k, dtype, variant, block_n, seed=0, gen=oracle.gemm_inputs_uniform, exact=None):
+    from peakgemm_b200 import capi
+
+    a, b = gen(m, n, k, dtype, seed)
+    c = helpers.garbage_like((m, n), dtype, "cuda")
+    capi.hgemm(c, a.cuda(), b.cuda(), variant=variant, block_n=block_n)
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0, "a kernel abandoned a bounded wait"
+    return helpers.check_gemm(c, a, b, exact_rows=exact)
+
+
+# ---- the smallest end-to-end case first: if this fails nothing else is worth running
+def test_single_tile_one_cta(cuda):
+    run_case(128, 256, 64, BF16, 1, 256)
+
+
+def test_single_tile_multi_kblock(cuda):
+    run_case(128, 256, 512, BF16, 1, 256)
+
+
+@pytest.mark.parametrize("block_n", [64, 128, 256])
+@pytest.mark.parametrize("dtype", [BF16, F16])
+def test_one_cta_variants(cuda, block_n, dtype):
+    run_case(512, 768, 1024, dtype, 1, block_n, seed=1)
+
+
+def test_pair_single_tile(cuda):
+    run_case(256, 256, 64, BF16, 2, 256)
+
+
+def test_pair_multi_kblock(cuda):
+    run_case(256, 256, 1024, BF16, 2, 256)
+
+
+@pytest.mark.parametrize("block_n", [64, 128, 256])
+@pytest.mark.parametrize("dtype", [BF16, F16])
+def test_pair_variants(cuda, block_n, dtype):
+    run_case(512, 768, 1024, dtype, 2, block_n, seed=1)
+
+
+# ---- persistence: more tiles than CTAs, several tiles per CTA, both accumulators reused
+@pytest.mark.parametrize("variant,block_n", [(1, 64), (1, 256), (2, 64), (2, 256)])
+def test_many_tiles_per_cta(cuda, variant, block_n):
+    run_case(2048, 4096, 256, BF16, variant, block_n, seed=2, exact=True)
+
+
+# ---- tails the reference never validates (it reads out of bounds there): TMA zero-fill / clipping
+@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("m,n,k", [
+    (16, 64, 64), (1, 8, 8), (130, 72, 40), (127, 248, 1000), (257, 264, 72), (300, 520, 136),
+    (128, 256, 8), (384, 8, 4096),
+])
+def test_tails(cuda, variant, m, n, k):
+    run_case(m, n, k, BF16, variant, 0 if variant == 1 else 128, seed=3)
+
+
+def test_empty_and_k0(cuda):
+    from peakgemm_b200 import capi
+
+    a = torch.zeros(0, 64, dtype=BF16, device="cuda")
+    b = torch.zeros(64, 64, dtype=BF16, device="cuda")
+    c = torch.zeros(0, 64, dtype=BF16, device="cuda")
+    capi.hgemm(c, a, b)                       # m == 0: no-op
+    a = torch.zeros(32, 0, dtype=BF16, device="cuda")
+    b = torch.zeros(64, 0, dtype=BF16, device="cuda")
+    c = helpers.garbage_like((32, 64), BF16, "cuda")
+    st = capi.lib().pg_hgemm(c.data_ptr(), 0, 0, 32, 64, 0, 0, 0, 64, capi.PG_BF16, None)
+    assert st == 0
+    torch.cuda.synchronize()
+    assert (c == 0).all()                     # k == 0: an empty sum
+
+
+def test_ldc_column_block(cuda):
+    """ldc > n: a column block written in place into a wider C (what the column-sharded caller does)."""
+    from peakgemm_b200 import capi
+
+    m, n, k, n_full = 384, 256, 512, 1024
+    a, b = oracle.gemm_inputs_uniform(m, n, k, BF16, 5)
+    full = helpers.garbage_like((m, n_full), BF16, "cuda")
+    before = full.clone()
+    block = full[:, 512:512 + n]
+    capi.hgemm(block, a.cuda(), b.cuda(), ldc=n_full)
+    torch.cuda.synchronize()
+    helpers.check_gemm(block, a, b)
+    assert torch.equal(full[:, :512], before[:, :512]) and torch.equal(full[:, 768:], before[:, 768:])
+
+
+def test_argument_errors(cuda):
+    from peakgemm_b200 import capi
+
+    L = capi.lib()
+    a = torch.zeros(128, 64, dtype=BF16, device="cuda")
+    p = a.data_ptr()
+    assert L.pg_hgemm(p, p, p, 128, 12, 64, 64, 64, 12, 1, None) == 3      # n % 8
+    assert L.pg_hgemm(p, p, p, 128, 64, 12, 12, 12, 64, 1, None) == 3      # k % 8
+    assert L.pg_hgemm(p + 2, p, p, 128, 64, 64, 64, 64, 64, 1, None) == 2  # misaligned
+    assert L.pg_hgemm(None, p, p, 128, 64, 64, 64, 64, 64, 1, None) == 1   # null
+    assert L.pg_hgemm(p, p, p, -1, 64, 64, 64, 64, 64, 1, None) == 1
+    assert L.pg_hgemm(p, p, p, 128, 64, 64, 64, 64, 64, 7, None) == 1      # dtype
+    assert L.pg_hgemm_ex(p, p, p, 128, 64, 64, 64, 64, 64, 1, 1, 96, None) == 1  # block_n
+
+
+# ---- BASELINE configurations
+def test_config1_bf16_2048(cuda):
+    """bf16 m=n=k=2048, U[-1,1], seed 0, automatic configuration, exact oracle too."""
+    err, tol = run_case(2048, 2048, 2048, BF16, 0, 0, seed=0, exact=True)
+    assert err <= 0.5  # pure bf16 output rounding at |C| <= 128 is <= 0.25
+
+
+@pytest.mark.parametrize("dtype", [BF16, F16])
+@pytest.mark.parametrize("size", [2048, 4096])
+def test_config2_square(cuda, size, dtype):
+    run_case(size, size, size, dtype, 0, 0, seed=1, exact=(size <= 2048))
+
+
+@pytest.mark.parametrize("dtype", [BF16, F16])
+def test_config2_8192_vs_device_oracle(cuda, dtype):
+    """Full size of the headline shape: every element against the device restatement of the
+    reference's naive kernel, and 64 sampled rows against the CPU oracle."""
+    from peakgemm_b200 import capi
+
+    s = 8192
+    a, b = oracle.gemm_inputs_uniform(s, s, s, dtype, 1)
+    ad, bd = a.cuda(), b.cuda()
+    c = helpers.garbage_like((s, s), dtype, "cuda")
+    capi.hgemm(c, ad, bd)
+    ref = helpers.gemm_naive_device(ad, bd)
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0
+    diff = (c.float() - ref.float()).abs().max().item()
+    assert diff <= oracle.reference_abs_tolerance(s), diff
+    rows = torch.arange(0, s, s // 64) + 7
+    helpers.check_gemm(c[rows], a[rows], b, exact_rows=False)
+
+
+@pytest.mark.parametrize("m", [16, 128, 1024])
+@pytest.mark.parametrize("n,k", [(4096, 4096), (14336, 4096), (4096, 14336)])
+def test_config3_skinny(cuda, m, n, k):
+    run_case(m, n, k, BF16, 0, 0, seed=2, gen=oracle.gemm_inputs_llm, exact=False)
+
+
+def test_config3_vocab_projection(cuda):
+    run_case(128, 128256, 4096, BF16, 0, 0, seed=2, gen=oracle.gemm_inputs_llm, exact=False)
+
+
+# ---- size-independent properties at full size
+def test_linearity_in_a(cuda):
+    """(2A) B^T == 2 (A B^T) exactly: scaling by a power of two commutes with every rounding."""
+    from peakgemm_b200 import capi
+
+    a, b = oracle.gemm_inputs_uniform(4096, 4096, 4096, BF16, 9)
+    ad, bd = a.cuda(), b.cuda()
+    c1 = torch.empty(4096, 4096, dtype=BF16, device="cuda")
+    c2 = torch.empty_like(c1)
+    capi.hgemm(c1, ad, bd)
+    capi.hgemm(c2, ad * 2, bd)
+    torch.cuda.synchronize()
+    assert torch.equal(c1.float() * 2, c2.float())
+
+
+def test_identity_b(cuda):
+    """B = I: C must reproduce A bit for bit (each sum has one non-zero term)."""
+    from peakgemm_b200 import capi
+
+    a, _ = oracle.gemm_inputs_uniform(1000, 8, 2048, BF16, 10)
+    eye = torch.eye(2048, dtype=BF16)
+    c = helpers.garbage_like((1000, 2048), BF16, "cuda")
+    capi.hgemm(c, a.cuda(), eye.cuda())
+    torch.cuda.synchronize()
+    assert torch.equal(c.cpu(), a)
+
+
+def test_deterministic(cuda):
+    from peakgemm_b200 import capi
+
+    a, b = oracle.gemm_inputs_uniform(1024, 1024, 4096, F16, 11)
+    ad, bd = a.cuda(), b.cuda()
+    outs = []
+    for _ in range(3):
+        c = torch.empty(1024, 1024, dtype=F16, device="cuda")
+        capi.hgemm(c, ad, bd)
+        outs.append(c)
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
