@@ -188,14 +188,14 @@ def time_cuda(fn, steps: int, warmup: int):
     return e0.elapsed_time(e1) / steps
 
 
-def rmsnorm_numbers(peaks: dict, steps: int, warmup: int) -> dict:
+def rmsnorm_numbers(peaks: dict, steps: int, warmup: int, rows: int = 32768) -> dict:
     """RMSNorm fwd/bwd achieved GB/s at [32768, H] bf16 (algorithmic bytes 4RH+4H and 6RH+8H)."""
     import torch
 
     from peakgemm_b200 import capi
 
     out = {}
-    R = 32768
+    R = rows
     for H in (4096, 8192):
         g = torch.Generator(device="cuda").manual_seed(3)
         x = torch.randn(R, H, device="cuda", generator=g).to(torch.bfloat16)
@@ -224,8 +224,16 @@ def main() -> None:
     ap.add_argument("--variant", type=int, default=0, help="GEMM kernel variant (0 auto, 1 one-CTA, 2 CTA pair)")
     ap.add_argument("--block-n", type=int, default=0)
     ap.add_argument("--no-extras", action="store_true", help="skip comparators, RMSNorm, e2e and CPU legs")
+    ap.add_argument("--size", type=int, default=8192,
+                    help="m=n=k of the GEMM; anything but 8192 is a profiling case, not the headline workload")
+    ap.add_argument("--only-rmsnorm", type=int, default=0, metavar="ROWS",
+                    help="profiling case: run only the RMSNorm kernels on [ROWS, 4096] and [ROWS, 8192] and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    global M, N, K, WORKLOAD
+    if args.size != 8192:
+        M = N = K = args.size
+        WORKLOAD = f"PROFILING CASE bf16 GEMM m=n=k={args.size} TN (not the headline workload)"
 
     if args.impl == "reference":
         run_reference_arm(args)
@@ -245,6 +253,10 @@ def main() -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     peaks = measured_peaks()
+    if args.only_rmsnorm:
+        print(json.dumps({"profiling_case": "rmsnorm", "rows": args.only_rmsnorm,
+                          "rmsnorm": rmsnorm_numbers(peaks, args.steps, args.warmup, rows=args.only_rmsnorm)}))
+        return
 
     # Inputs: generated on the device from seed 1 (the parity tests use CPU-generated copies of the
     # same distribution); rank r holds A and the r-th 8192-column block of B.
@@ -294,7 +306,8 @@ def main() -> None:
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD if world == 1 else WORKLOAD + f"; x{world} ranks, rank r owns column block r "
-                   f"of B[{N * world},{K}] (A replicated), no gather", "l2": "inputs+output 403 MB per step > 126 MB L2",
+                   f"of B[{N * world},{K}] (A replicated), no gather",
+                   "l2": f"inputs+output {6 * M * N / 1e6:.0f} MB per step vs 126 MB L2",
                    "kernel": f"variant={args.variant} block_n={args.block_n} (0 = automatic)"},
         "gpu_launches": args.steps,
         "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks[peak_key], "unit": "TFLOP/s",

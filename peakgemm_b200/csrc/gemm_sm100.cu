@@ -49,6 +49,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "gemm_sm100.h"
 #include "ptx.cuh"
@@ -68,6 +69,14 @@ constexpr uint32_t kStoreCols = 64;     // columns per TMA store box (128 bytes)
 constexpr uint32_t kStoreRows = 32;     // rows per TMA store box (one warp's lanes)
 constexpr uint32_t kStageBufBytes = kStoreRows * kStoreCols * 2;  // 4096
 constexpr uint64_t kWaitTimeoutNs = 2000000000ull;                // 2 s
+constexpr uint32_t kDefaultFlags = 0;
+
+// Tuning switches (kernel argument `flags`).
+enum : uint32_t {
+    kFlagEpiLanePoll = 1u,       // epilogue: one lane polls acc_full with a back-off
+    kFlagStoreEvictFirst = 2u,   // C stores carry an L2 evict-first hint
+    kFlagLoadEvictLast = 4u,     // A/B loads carry an L2 evict-last hint
+};
 
 // Codes written to the device status word (role that gave up).
 enum : int {
@@ -103,22 +112,41 @@ struct WaitCtx {
     int *status;                    // global memory
 };
 
-// Bounded mbarrier wait.  Returns false if the wait was abandoned.
-template <bool CLUSTER_ACQUIRE>
+// Bounded mbarrier wait.  Returns false if the wait was abandoned.  The clock is
+// only consulted every 1024 failed probes (each probe already suspends the thread
+// for a hardware-defined interval), so the common short wait costs nothing extra.
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, const WaitCtx &ctx, int code) {
-    auto probe = [&]() {
-        if constexpr (CLUSTER_ACQUIRE) return mbar_try_wait_cluster(bar, parity);
-        else return mbar_try_wait(bar, parity);
-    };
-    if (probe()) return true;
-    if (*ctx.abort_flag) return false;
-    const uint64_t t0 = globaltimer_ns();
+    if (mbar_try_wait(bar, parity)) return true;
+    uint64_t t0 = 0;
     uint32_t spins = 0;
     while (true) {
-        if (probe()) return true;
-        if ((++spins & 63u) == 0) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 1023u) == 0) {
             if (*ctx.abort_flag) return false;
-            if (globaltimer_ns() - t0 > kWaitTimeoutNs) {
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitTimeoutNs) {
+                *ctx.abort_flag = 1;
+                atomicCAS(ctx.status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+// Like wait_bar, for waits that normally last a whole tile: sleeps between probes.
+__device__ __forceinline__ bool wait_bar_backoff(uint32_t bar, uint32_t parity, const WaitCtx &ctx, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    uint64_t t0 = 0;
+    uint32_t spins = 0;
+    while (true) {
+        __nanosleep(200);
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 1023u) == 0) {
+            if (*ctx.abort_flag) return false;
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitTimeoutNs) {
                 *ctx.abort_flag = 1;
                 atomicCAS(ctx.status, 0, code);
                 return false;
@@ -129,8 +157,7 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, const Wa
 
 // Grouped raster: tile t -> (mi, ni).  Tiles are numbered down the rows of a band
 // of kGroupM tile rows first, then across the columns, band after band.
-template <uint32_t kGroupM>
-__device__ __forceinline__ void tile_coords(uint32_t t, uint32_t m_tiles, uint32_t n_tiles,
+__device__ __forceinline__ void tile_coords(uint32_t kGroupM, uint32_t t, uint32_t m_tiles, uint32_t n_tiles,
                                             uint32_t &mi, uint32_t &ni) {
     const uint32_t per_band = kGroupM * n_tiles;
     const uint32_t band = t / per_band;
@@ -146,9 +173,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                      const __grid_constant__ CUtensorMap tm_b,
                      const __grid_constant__ CUtensorMap tm_c,
-                     uint32_t M, uint32_t N, uint32_t K, int *status) {
+                     uint32_t M, uint32_t N, uint32_t K, uint32_t group_m, uint32_t flags, int *status) {
     using C = Cfg<CTA_GROUP, BN, STAGES>;
-    constexpr uint32_t kGroupM = 16 / CTA_GROUP;
     constexpr uint32_t kTileM = kBM * CTA_GROUP;
 
     extern __shared__ uint8_t smem_raw[];
@@ -215,15 +241,16 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
             const uint32_t peer_empty0 = (CTA_GROUP == 2) ? mapa(bar_empty, 1) : 0u;
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            const uint64_t pol_load = l2_policy_evict_last();
             for (uint32_t t = worker; ok && t < total_tiles; t += workers) {
                 uint32_t mi, ni;
-                tile_coords<kGroupM>(t, m_tiles, n_tiles, mi, ni);
+                tile_coords(group_m, t, m_tiles, n_tiles, mi, ni);
                 const int32_t row_a = static_cast<int32_t>(mi * kTileM + rank * kBM);
                 const int32_t row_b = static_cast<int32_t>(ni * BN + rank * C::kBRows);
                 for (uint32_t kb = 0; kb < k_blocks; ++kb) {
                     if (leader) {
                         // wait until the MMAs that read this stage have completed
-                        ok = wait_bar<false>(bar_empty + stage * 8, phase ^ 1u, ctx, kStProducerEmpty);
+                        ok = wait_bar(bar_empty + stage * 8, phase ^ 1u, ctx, kStProducerEmpty);
                         if (!ok) break;
                         if constexpr (CTA_GROUP == 2) {
                             mbar_arrive_cluster(peer_empty0 + stage * 8);   // relay to the peer
@@ -232,13 +259,21 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                             mbar_arrive_expect_tx(bar_full + stage * 8, C::kStageBytes);
                         }
                     } else {
-                        ok = wait_bar<true>(bar_empty + stage * 8, phase, ctx, kStProducerEmpty);
+                        ok = wait_bar(bar_empty + stage * 8, phase, ctx, kStProducerEmpty);
                         if (!ok) break;
                     }
                     const uint32_t dst_a = smem_base + C::kOffA + stage * C::kABytes;
                     const uint32_t dst_b = smem_base + C::kOffB + stage * C::kBBytes;
                     const int32_t kx = static_cast<int32_t>(kb * kBK);
-                    if constexpr (CTA_GROUP == 2) {
+                    if (flags & kFlagLoadEvictLast) {
+                        if constexpr (CTA_GROUP == 2) {
+                            tma_load_2d_pair_hint(dst_a, &tm_a, full0 + stage * 8, kx, row_a, pol_load);
+                            tma_load_2d_pair_hint(dst_b, &tm_b, full0 + stage * 8, kx, row_b, pol_load);
+                        } else {
+                            tma_load_2d_hint(dst_a, &tm_a, bar_full + stage * 8, kx, row_a, pol_load);
+                            tma_load_2d_hint(dst_b, &tm_b, bar_full + stage * 8, kx, row_b, pol_load);
+                        }
+                    } else if constexpr (CTA_GROUP == 2) {
                         tma_load_2d_pair(dst_a, &tm_a, full0 + stage * 8, kx, row_a);
                         tma_load_2d_pair(dst_b, &tm_b, full0 + stage * 8, kx, row_b);
                     } else {
@@ -258,12 +293,12 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
             bool ok = true;
             for (uint32_t t = worker; ok && t < total_tiles; t += workers) {
                 // the epilogue must have drained this accumulator (passes at once the first two times)
-                ok = wait_bar<CTA_GROUP == 2>(bar_acc_empty + acc * 8, acc_phase ^ 1u, ctx, kStMmaAccEmpty);
+                ok = wait_bar(bar_acc_empty + acc * 8, acc_phase ^ 1u, ctx, kStMmaAccEmpty);
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t tmem_d = tmem_base + acc * BN;
                 for (uint32_t kb = 0; kb < k_blocks; ++kb) {
-                    ok = wait_bar<false>(bar_full + stage * 8, phase, ctx, kStMmaFull);
+                    ok = wait_bar(bar_full + stage * 8, phase, ctx, kStMmaFull);
                     if (!ok) break;
                     tc_fence_after_sync();
                     const uint64_t da = smem_desc_k_sw128(smem_base + C::kOffA + stage * C::kABytes);
@@ -292,11 +327,18 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         const uint32_t peer_acc_full = (CTA_GROUP == 2) ? mapa(bar_acc_full, 1) : 0u;
         uint32_t acc = 0, acc_phase = 0, nbuf = 0;
         bool ok = true;
+        const uint64_t pol_store = l2_policy_evict_first();
         for (uint32_t t = worker; ok && t < total_tiles; t += workers) {
             uint32_t mi, ni;
-            tile_coords<kGroupM>(t, m_tiles, n_tiles, mi, ni);
-            ok = wait_bar<CTA_GROUP == 2>(bar_acc_full + acc * 8, acc_phase, ctx, kStEpiAccFull);
-            ok = __all_sync(0xffffffffu, ok);
+            tile_coords(group_m, t, m_tiles, n_tiles, mi, ni);
+            if (flags & kFlagEpiLanePoll) {
+                // one lane polls, with a back-off: the other 31 (x4 warps) sleep at the warp barrier
+                if (lane == 0) ok = wait_bar_backoff(bar_acc_full + acc * 8, acc_phase, ctx, kStEpiAccFull);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+            } else {
+                ok = wait_bar(bar_acc_full + acc * 8, acc_phase, ctx, kStEpiAccFull);
+                ok = __all_sync(0xffffffffu, ok);
+            }
             if (!ok) break;
             if constexpr (CTA_GROUP == 2) {
                 if (leader && e == 0 && lane == 0) mbar_arrive_cluster(peer_acc_full + acc * 8);  // relay
@@ -339,8 +381,13 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                 __syncwarp();
                 const uint32_t col0 = ni * BN + ch * kStoreCols;
                 if (lane == 0) {
-                    if (row0 < M && col0 < N)
-                        tma_store_2d(&tm_c, sbuf, static_cast<int32_t>(col0), static_cast<int32_t>(row0));
+                    if (row0 < M && col0 < N) {
+                        if (flags & kFlagStoreEvictFirst)
+                            tma_store_2d_hint(&tm_c, sbuf, static_cast<int32_t>(col0), static_cast<int32_t>(row0),
+                                              pol_store);
+                        else
+                            tma_store_2d(&tm_c, sbuf, static_cast<int32_t>(col0), static_cast<int32_t>(row0));
+                    }
                     bulk_commit_group();
                 }
                 nbuf ^= 1u;
@@ -478,8 +525,13 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, cudaStream_t stream) 
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    uint32_t group_m = 16 / CTA_GROUP, flags = kDefaultFlags;
+    if (const char *e = getenv("PEAKGEMM_TUNE_GROUP_M")) group_m = static_cast<uint32_t>(atoi(e));
+    if (const char *e = getenv("PEAKGEMM_TUNE_FLAGS")) flags = static_cast<uint32_t>(atoi(e));
+    if (group_m < 1) group_m = 1;
     return cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b, tm_c, static_cast<uint32_t>(g.m),
-                              static_cast<uint32_t>(g.n), static_cast<uint32_t>(g.k), d.status_word);
+                              static_cast<uint32_t>(g.n), static_cast<uint32_t>(g.k), group_m, flags,
+                              d.status_word);
 }
 
 template <int CTA_GROUP, int BN, int STAGES>

@@ -1,7 +1,7 @@
 """GPU parity of the tcgen05 GEMM with the oracle, called through the C ABI (pg_hgemm_ex).
 
-Bound for every case: max|C - C_ref| <= 2e-2 * sqrt(k/4096) * max|C_ref| (C_ref = fp32-accumulated
-product of the same 16-bit inputs), plus the reference test's own bound 0.5*k/4096 against the exact
+Bound for every case: max|C - C_ref| <= (2e-2 * sqrt(k/4096) + eps_out) * max|C_ref| (C_ref = fp32-accumulated
+product of the same 16-bit inputs; eps_out = one rounding step of the output type), plus the reference test's own bound 0.5*k/4096 against the exact
 k-ordered oracle where that is affordable.  Inputs are generated on the CPU from fixed seeds, C is
 pre-filled with garbage (the reference's tests do the same: test/test_gemm.py:32-34).
 """

@@ -31,7 +31,8 @@ def _stream():
 def test_cpu_oracle_equals_reference_naive_kernel(cuda, m, n, k, dtype):
     a, b = oracle.gemm_inputs_uniform(m, n, k, dtype, 31)
     c = helpers.garbage_like((m, n), dtype, "cuda")
-    r = _ref().ref_sgemm_naive(c.data_ptr(), a.cuda().data_ptr(), b.cuda().data_ptr(), m, n, k,
+    ad, bd = a.cuda(), b.cuda()
+    r = _ref().ref_sgemm_naive(c.data_ptr(), ad.data_ptr(), bd.data_ptr(), m, n, k,
                                int(dtype == torch.bfloat16), _stream())
     assert r == 0
     torch.cuda.synchronize()
