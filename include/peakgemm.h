@@ -90,9 +90,9 @@ int pg_hgemm_ex(void *c, const void *a, const void *b,
                 int dtype, int variant, int block_n, void *stream);
 
 /*
- * Device-side status word of the GEMM kernels on the current device: 0 if no
- * kernel has given up on a bounded wait since the last call, otherwise a code
- * that names the waiting role.  Synchronises `stream`, reads the word, clears
+ * Device-side status word of the kernels on the current device: 0 if no kernel
+ * has given up on a bounded wait since the last call, otherwise a code that names
+ * the waiting role (1-4: GEMM producer / MMA / epilogue; 11-12: RMSNorm).  Synchronises `stream`, reads the word, clears
  * it.  Returns PG_OK and writes *device_status, or an error status.
  */
 int pg_device_status(int *device_status, void *stream);

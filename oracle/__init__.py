@@ -131,6 +131,36 @@ def rmsnorm_bwd(dy: torch.Tensor, x: torch.Tensor, gamma: torch.Tensor, eps: flo
     return dx, dgamma
 
 
+def rmsnorm_bwd_dx_slack(dy: torch.Tensor, x: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """Per-element absolute slack for dx on top of one 16-bit ulp: the fp32 error of the formula itself.
+
+    dx = rstd * (g - xhat * c), c = mean_j(g * xhat), subtracts two fp32 numbers that can nearly cancel,
+    and c is itself a sum of h terms of mixed sign.  Two correct fp32 evaluations that differ only in the
+    order of the row reductions can therefore differ by about
+        2^-24 * rstd * ( 8 |g| + 8 |xhat c| + |xhat| * sqrt(h) * mean_j |g xhat| )
+    (a few roundings on each operand, plus the summation error of c, ~ sqrt(h) * 2^-24 * mean|terms|),
+    which exceeds one 16-bit ulp only where dx cancelled to almost nothing.  This returns that bound.
+    """
+    xf, dyf, g32 = x.float(), dy.float(), gamma.float()
+    h = x.shape[-1]
+    rstd = torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + eps)
+    xhat = xf * rstd
+    g = dyf * g32
+    gx = g * xhat
+    c = gx.mean(dim=-1, keepdim=True)
+    c_err = math.sqrt(h) * gx.abs().mean(dim=-1, keepdim=True)
+    return 2.0 ** -24 * rstd * (8.0 * g.abs() + 8.0 * (xhat * c).abs() + xhat.abs() * c_err)
+
+
+def within_ulp_or_slack(out: torch.Tensor, ref_fp32: torch.Tensor, slack: torch.Tensor | None = None,
+                        ulps: int = 1) -> torch.Tensor:
+    """Elementwise: out within `ulps` 16-bit ulps of round(ref), or |out - ref| <= slack."""
+    ok = ulp_distance_16(out, ref_fp32) <= ulps
+    if slack is not None:
+        ok |= (out.float() - ref_fp32).abs() <= slack + (ref_fp32.to(out.dtype).float() - ref_fp32).abs()
+    return ok
+
+
 def ulp_distance_16(out: torch.Tensor, ref_fp32: torch.Tensor) -> torch.Tensor:
     """|out - round(ref)| in units of out's 16-bit ulp at round(ref), elementwise (int64).
 

@@ -79,8 +79,13 @@ int pg_hgemm(void *c, const void *a, const void *b, int64_t m, int64_t n, int64_
 int pg_device_status(int *device_status, void *stream) {
     if (!device_status) return PG_ERR_BAD_ARG;
     cudaError_t e = cudaSuccess;
-    const int r = pg::gemm_device_status(device_status, static_cast<cudaStream_t>(stream), &e);
-    return from_launch(r, e);
+    int gemm = 0, rms = 0;
+    const int r = pg::gemm_device_status(&gemm, static_cast<cudaStream_t>(stream), &e);
+    if (r != pg::kLaunchOk) return from_launch(r, e);
+    e = pg::rmsnorm_device_status(&rms, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(e);
+    *device_status = gemm != 0 ? gemm : rms;
+    return PG_OK;
 }
 
 int pg_rmsnorm_fwd(void *y, const void *x, const float *gamma, int64_t rows, int64_t h, float eps,

@@ -558,7 +558,8 @@ void choose_config(const GemmArgs &g, int sm_count, int *variant, int *block_n) 
             const int64_t tiles = ((g.m + tile_m - 1) / tile_m) * ((g.n + bn - 1) / bn);
             const int64_t workers = sm_count / v;
             const int64_t waves = (tiles + workers - 1) / workers;
-            const double eff = (bn == 256 ? 1.0 : bn == 128 ? 0.9 : 0.75) * (v == 2 ? 1.05 : 1.0);
+            // measured at 8192^3: block_n 128 runs at ~0.72 of block_n 256 per flop (operand traffic per flop doubles)
+            const double eff = (bn == 256 ? 1.0 : bn == 128 ? 0.72 : 0.45) * (v == 2 ? 1.06 : 1.0);
             const double cost = static_cast<double>(waves) * bn / eff;
             if (cost < best) { best = cost; best_v = v; best_bn = bn; }
         }

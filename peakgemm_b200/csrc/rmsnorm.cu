@@ -365,6 +365,10 @@ int64_t rmsnorm_max_h() { return 1024 * 8 * 8; }
 
 // Number of CTAs (= partial rows) the backward kernel uses for this shape.
 cudaError_t rmsnorm_bwd_ctas(int64_t rows, int64_t h, bool bf16, int *ctas) {
+    if (rmsnorm_staged_supported(h, true)) {
+        int grid = 0;
+        return rmsnorm_staged_ctas(rows, h, true, &grid, ctas);
+    }
     const BwdPlan p = bwd_plan(h);
     if (p.threads == 0) { *ctas = 0; return cudaSuccess; }
     int sms = 0;
@@ -382,6 +386,7 @@ cudaError_t rmsnorm_bwd_ctas(int64_t rows, int64_t h, bool bf16, int *ctas) {
 }
 
 cudaError_t rmsnorm_fwd_launch(const RmsFwdArgs &a, cudaStream_t stream) {
+    if (rmsnorm_staged_supported(a.h, false)) return rmsnorm_staged_fwd(a, stream);
     const int h8 = static_cast<int>(a.h / 8);
     const float h_f = static_cast<float>(a.h);
     int sms = 0;
@@ -425,9 +430,15 @@ cudaError_t rmsnorm_fwd_launch(const RmsFwdArgs &a, cudaStream_t stream) {
 }
 
 cudaError_t rmsnorm_bwd_launch(const RmsBwdArgs &a, int ctas, cudaStream_t stream) {
-    const BwdPlan p = bwd_plan(a.h);
-    if (p.threads == 0 || ctas < 1) return cudaErrorInvalidValue;
-    cudaError_t e = PG_BWD_DISPATCH(p, bwd_launch, a, ctas, stream);
+    cudaError_t e;
+    if (rmsnorm_staged_supported(a.h, true)) {
+        if (ctas < 1) return cudaErrorInvalidValue;
+        e = rmsnorm_staged_bwd(a, stream);
+    } else {
+        const BwdPlan p = bwd_plan(a.h);
+        if (p.threads == 0 || ctas < 1) return cudaErrorInvalidValue;
+        e = PG_BWD_DISPATCH(p, bwd_launch, a, ctas, stream);
+    }
     if (e != cudaSuccess) return e;
     const int h4 = static_cast<int>(a.h / 4);
     rmsnorm_dgamma_reduce_kernel<<<(h4 + 31) / 32, 1024, 0, stream>>>(

@@ -29,10 +29,18 @@ struct RmsBwdArgs {
 // Largest h the backward kernel supports.
 int64_t rmsnorm_max_h();
 
-// CTAs (= fp32 partial rows of dgamma) the backward kernel uses for this shape on the current device.
+// fp32 partial rows of dgamma the backward kernel writes for this shape on the current device.
 cudaError_t rmsnorm_bwd_ctas(int64_t rows, int64_t h, bool bf16, int *ctas);
 
 cudaError_t rmsnorm_fwd_launch(const RmsFwdArgs &a, cudaStream_t stream);
 cudaError_t rmsnorm_bwd_launch(const RmsBwdArgs &a, int ctas, cudaStream_t stream);
+
+// Bulk-copy staged variants (rmsnorm_staged.cu), used for 2048 <= h <= 16384.
+bool rmsnorm_staged_supported(int64_t h, bool bwd);
+cudaError_t rmsnorm_staged_ctas(int64_t rows, int64_t h, bool bwd, int *ctas, int *partial_rows);
+cudaError_t rmsnorm_staged_fwd(const RmsFwdArgs &a, cudaStream_t stream);
+cudaError_t rmsnorm_staged_bwd(const RmsBwdArgs &a, cudaStream_t stream);   // writes the partial rows only
+// Synchronises the stream, returns and clears the staged kernels' device status word.
+cudaError_t rmsnorm_device_status(int *out, cudaStream_t stream);
 
 }  // namespace pg

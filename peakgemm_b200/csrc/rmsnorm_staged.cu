@@ -1,0 +1,463 @@
+// RMSNorm forward / backward, bulk-copy staged variant for 256 <= h <= 16384.
+//
+// HBM-bound work: what matters is that every SM keeps enough bytes in flight all
+// the time and that no latency chain on the compute side is exposed.
+//   * One producer thread per CTA streams rows of x (and of dy for the backward
+//     pass) into a ring of shared-memory slots with cp.async.bulk (16-byte aligned,
+//     completion counted on an mbarrier), up to 16 rows ahead: bytes in flight do
+//     not depend on registers or occupancy.
+//   * The consumer warps are split into kG independent groups of T threads.  Group
+//     g takes every kG-th row of the CTA; a row's chain (shared -> registers,
+//     warp-shuffle + cross-warp reduction through ONE named barrier of the group,
+//     scaling, 128-bit streaming stores) overlaps with the other groups' chains.
+//   * Each thread owns VPT column vectors (8 elements each) for the whole kernel:
+//     gamma is read from a shared-memory copy and, in the backward pass, the
+//     thread's share of dgamma accumulates in registers.  A slot is released as soon
+//     as it has been copied into registers.
+// Backward: at the end the groups fold their dgamma shares, in a fixed order, into
+// one fp32 partial row per CTA; the fixed-order column reduction kernel in
+// rmsnorm.cu sums the CTAs' rows (deterministic).
+//
+// Every mbarrier wait is bounded (same scheme as the GEMM kernel).
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdlib.h>
+
+#include "ptx.cuh"
+#include "rmsnorm.h"
+
+namespace pg {
+
+using namespace ptx;
+
+namespace {
+
+constexpr int kMaxConsumers = 512;                // consumer threads per CTA (kG groups x T threads)
+constexpr int kThreads = kMaxConsumers + 32;      // + producer warp
+constexpr int kMaxStages = 16;
+constexpr uint64_t kWaitTimeoutNs = 2000000000ull;
+constexpr uint32_t kSmemBudget = 200 * 1024;      // bytes of dynamic shared memory we ask for at most
+
+enum : int { kStRmsProducer = 11, kStRmsConsumer = 12 };
+
+__device__ int g_rms_status_word;
+
+struct WaitCtx {
+    volatile uint32_t *abort_flag;
+    int *status;
+};
+
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, const WaitCtx &ctx, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    uint64_t t0 = 0;
+    uint32_t spins = 0;
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 1023u) == 0) {
+            if (*ctx.abort_flag) return false;
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitTimeoutNs) {
+                *ctx.abort_flag = 1;
+                atomicCAS(ctx.status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+// 1-D bulk copy global -> shared; both addresses 16-byte aligned, bytes % 16 == 0.
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+// Named barrier `id` over `nthreads` consumer threads that also ORs a predicate across
+// them, so that "somebody abandoned a wait" is decided identically by the whole group.
+__device__ __forceinline__ bool group_barrier_or(uint32_t id, uint32_t nthreads, bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %1, 0;\n\t"
+        "bar.red.or.pred p, %2, %3, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(r)
+        : "r"(static_cast<uint32_t>(pred)), "r"(id), "r"(nthreads)
+        : "memory");
+    return r != 0;
+}
+
+template <bool BF16>
+__device__ __forceinline__ void unpack8(const uint4 &v, float (&f)[8]) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if constexpr (BF16) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        } else {
+            const float2 t = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+            f[2 * i] = t.x;
+            f[2 * i + 1] = t.y;
+        }
+    }
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    return make_uint4(pack2<BF16>(f[0], f[1]), pack2<BF16>(f[2], f[3]), pack2<BF16>(f[4], f[5]),
+                      pack2<BF16>(f[6], f[7]));
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Shared memory: [gamma: h fp32][slots x (x row [+ dy row])][red][barriers][abort flag]
+struct Layout {
+    uint32_t off_slot, slot_bytes, row_bytes, off_red, off_bar, total;
+};
+
+__host__ __device__ inline Layout make_layout(int h, bool bwd, int stages) {
+    Layout l;
+    l.off_slot = static_cast<uint32_t>(h) * 4;                       // gamma; a multiple of 32 bytes
+    l.row_bytes = static_cast<uint32_t>(h) * 2;
+    l.slot_bytes = l.row_bytes * (bwd ? 2 : 1);
+    l.off_red = l.off_slot + stages * l.slot_bytes;
+    l.off_bar = l.off_red + 2 * 16 * 2 * static_cast<uint32_t>(sizeof(float));   // [2 buffers][16 warps][2]
+    l.total = l.off_bar + 2 * stages * 8 + 16;
+    return l;
+}
+
+// T threads per group (a multiple of 32), G groups, VPT * T >= h / 8.
+template <bool BWD, int VPT, bool BF16>
+__global__ void __launch_bounds__(kThreads, 1)
+rms_staged_kernel(uint4 *__restrict__ out, float *__restrict__ partial, const uint4 *__restrict__ x,
+                  const uint4 *__restrict__ dy, const float *__restrict__ gamma, int64_t rows, int h8,
+                  float h_f, float eps, int stages, int T, int G, int *status) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int h = h8 * 8;
+    const Layout L = make_layout(h, BWD, stages);
+    const uint32_t sbase = smem_u32(smem);
+    const float *s_gamma = reinterpret_cast<const float *>(smem);
+    float(*s_red)[16][2] = reinterpret_cast<float(*)[16][2]>(smem + L.off_red);
+    const uint32_t bar_full = sbase + L.off_bar;
+    const uint32_t bar_empty = bar_full + stages * 8;
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem + L.off_bar + 2 * stages * 8);
+    const WaitCtx ctx{abort_flag, status};
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int consumers = T * G;
+    const int group_warps = T >> 5;
+    // rows of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...; its i-th row goes to slot i % stages, group i % G
+    const int64_t my_rows = rows > blockIdx.x ? (rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(bar_full + s * 8, 1);                 // producer's arrive.expect_tx (+ copied bytes)
+            mbar_init(bar_empty + s * 8, group_warps);      // one arrive per warp of the consuming group
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    for (int i = threadIdx.x; i < h / 4; i += kThreads)
+        reinterpret_cast<float4 *>(smem)[i] = __ldg(reinterpret_cast<const float4 *>(gamma) + i);
+    __syncthreads();
+
+    const bool is_consumer = threadIdx.x < consumers;
+    const int g = is_consumer ? threadIdx.x / T : 0;   // group (warps of a group are contiguous)
+    const int t = threadIdx.x - g * T;                 // thread within the group
+    float acc[VPT][8];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[j][e] = 0.f;
+
+    if (threadIdx.x >= kMaxConsumers) {
+        // ===== producer =====
+        if (lane == 0) {
+            int slot = 0;
+            uint32_t phase = 0;
+            for (int64_t i = 0; i < my_rows; ++i) {
+                if (!wait_bar(bar_empty + slot * 8, phase ^ 1u, ctx, kStRmsProducer)) break;
+                const int64_t row = blockIdx.x + i * gridDim.x;
+                mbar_arrive_expect_tx(bar_full + slot * 8, L.slot_bytes);
+                const uint32_t dst = sbase + L.off_slot + slot * L.slot_bytes;
+                bulk_load(dst, x + row * h8, L.row_bytes, bar_full + slot * 8);
+                if constexpr (BWD) bulk_load(dst + L.row_bytes, dy + row * h8, L.row_bytes, bar_full + slot * 8);
+                if (++slot == stages) { slot = 0; phase ^= 1u; }
+            }
+        }
+        __syncwarp();
+    } else if (is_consumer) {
+        // ===== consumers =====
+        const int gw = t >> 5;                   // warp within the group
+        int it = 0;
+        for (int64_t i = g; i < my_rows; i += G, it ^= 1) {
+            const int slot = static_cast<int>(i % stages);
+            const uint32_t phase = static_cast<uint32_t>(i / stages) & 1u;
+            const int64_t row = blockIdx.x + i * gridDim.x;
+            bool ok = wait_bar(bar_full + slot * 8, phase, ctx, kStRmsConsumer);
+            ok = __all_sync(0xffffffffu, ok);
+            // A warp that gave up still walks to the barrier below (on zeros), where the whole group
+            // learns of it together; leaving here would strand the others at that barrier.
+            const uint8_t *sx = smem + L.off_slot + slot * L.slot_bytes;
+            uint4 xv[VPT], dv[VPT];
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const int idx = t + T * j;
+                const bool in = ok && (idx < h8);
+                xv[j] = in ? reinterpret_cast<const uint4 *>(sx)[idx] : make_uint4(0, 0, 0, 0);
+                if constexpr (BWD)
+                    dv[j] = in ? reinterpret_cast<const uint4 *>(sx + L.row_bytes)[idx] : make_uint4(0, 0, 0, 0);
+            }
+            // the row lives in registers now: hand the slot back to the producer
+            __syncwarp();
+            if (lane == 0 && ok) mbar_arrive(bar_empty + slot * 8);
+
+            float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const int idx = t + T * j;
+                float xf[8];
+                unpack8<BF16>(xv[j], xf);
+                if constexpr (BWD) {
+                    float df[8];
+                    unpack8<BF16>(dv[j], df);
+                    if (idx < h8) {
+                        const float4 g0 = reinterpret_cast<const float4 *>(s_gamma)[2 * idx];
+                        const float4 g1 = reinterpret_cast<const float4 *>(s_gamma)[2 * idx + 1];
+                        const float gm[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            s1 = fmaf(xf[e], xf[e], s1);
+                            s2 = fmaf(df[e] * gm[e], xf[e], s2);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) s1 = fmaf(xf[e], xf[e], s1);
+                }
+            }
+            s1 = warp_sum(s1);
+            if constexpr (BWD) s2 = warp_sum(s2);
+            if (lane == 0) {
+                s_red[it][warp][0] = s1;
+                s_red[it][warp][1] = s2;
+            }
+            // One barrier per row: s_red is double-buffered, and buffer `it` is only rewritten two
+            // rows later, after every thread of the group has passed the barrier in between.
+            if (group_barrier_or(1 + g, T, !ok || *abort_flag != 0)) break;
+            float S1 = 0.f, S2 = 0.f;
+            for (int w = 0; w < group_warps; ++w) {
+                S1 += s_red[it][warp - gw + w][0];
+                if constexpr (BWD) S2 += s_red[it][warp - gw + w][1];
+            }
+            const float rstd = 1.0f / sqrtf(S1 / h_f + eps);
+            const float cm = (S2 * rstd) / h_f;     // backward: mean_j(g * xhat)
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const int idx = t + T * j;
+                if (idx < h8) {
+                    const float4 g0 = reinterpret_cast<const float4 *>(s_gamma)[2 * idx];
+                    const float4 g1 = reinterpret_cast<const float4 *>(s_gamma)[2 * idx + 1];
+                    const float gm[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+                    float xf[8], o[8];
+                    unpack8<BF16>(xv[j], xf);
+                    if constexpr (BWD) {
+                        float df[8];
+                        unpack8<BF16>(dv[j], df);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const float xhat = xf[e] * rstd;
+                            o[e] = rstd * (df[e] * gm[e] - xhat * cm);
+                            acc[j][e] = fmaf(df[e], xhat, acc[j][e]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) o[e] = (xf[e] * rstd) * gm[e];
+                    }
+                    __stcs(out + row * h8 + idx, pack8<BF16>(o));
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if constexpr (BWD) {
+        // The ring is idle now: fold the groups' dgamma shares into one fp32 row in shared memory,
+        // group after group (a fixed order), and write ONE partial row per CTA.  Done even after an
+        // abandoned wait, so the reduction kernel never reads uninitialised scratch.
+        float *s_acc = reinterpret_cast<float *>(smem + L.off_slot);
+        for (int gg = 0; gg < G; ++gg) {
+            if (is_consumer && g == gg) {
+#pragma unroll
+                for (int j = 0; j < VPT; ++j) {
+                    const int idx = t + T * j;
+                    if (idx < h8) {
+                        float4 *p = reinterpret_cast<float4 *>(s_acc) + 2 * idx;
+                        float4 a0 = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
+                        float4 a1 = make_float4(acc[j][4], acc[j][5], acc[j][6], acc[j][7]);
+                        if (gg > 0) {
+                            const float4 o0 = p[0], o1 = p[1];
+                            a0.x += o0.x; a0.y += o0.y; a0.z += o0.z; a0.w += o0.w;
+                            a1.x += o1.x; a1.y += o1.y; a1.z += o1.z; a1.w += o1.w;
+                        }
+                        p[0] = a0;
+                        p[1] = a1;
+                    }
+                }
+            }
+            __syncthreads();
+        }
+        float4 *prow = reinterpret_cast<float4 *>(partial + static_cast<int64_t>(blockIdx.x) * h);
+        for (int i = threadIdx.x; i < h / 4; i += kThreads) prow[i] = reinterpret_cast<const float4 *>(s_acc)[i];
+    }
+    if (*abort_flag) __nanosleep(50000);   // let bulk copies still in flight land before shared memory goes away
+}
+
+struct Plan {
+    bool ok;
+    int vpt, T, G, stages;
+    uint32_t smem;
+};
+
+Plan make_plan(int64_t h, bool bwd) {
+    Plan p{false, 0, 0, 0, 0, 0};
+    const int64_t h8 = h / 8;
+    if (h8 < 32 || h8 > 2048) return p;
+    // aim at 4 vectors per thread; groups of 32..256 threads
+    int T = static_cast<int>((h8 / 4 + 31) / 32 * 32);
+    if (T < 32) T = 32;
+    if (T > 256) T = 256;
+    const int need = static_cast<int>((h8 + T - 1) / T);
+    p.vpt = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
+    p.T = T;
+    p.G = kMaxConsumers / T;
+    if (p.G > 8) p.G = 8;
+    for (int s = kMaxStages; s >= 2; --s) {
+        const Layout l = make_layout(static_cast<int>(h), bwd, s);
+        if (l.total <= kSmemBudget) {
+            p.stages = s;
+            p.smem = l.total;
+            p.ok = true;
+            return p;
+        }
+    }
+    return p;
+}
+
+int g_sms[64] = {};
+int *g_status_ptr[64] = {};
+
+cudaError_t device_setup(int *sms, int **status) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (g_sms[dev] == 0) {
+        if ((e = cudaDeviceGetAttribute(&g_sms[dev], cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+        void *p = nullptr;
+        if ((e = cudaGetSymbolAddress(&p, g_rms_status_word)) != cudaSuccess) return e;
+        g_status_ptr[dev] = static_cast<int *>(p);
+    }
+    *sms = g_sms[dev];
+    *status = g_status_ptr[dev];
+    return cudaSuccess;
+}
+
+template <bool BWD, int VPT, bool BF16>
+cudaError_t launch_one(void *out, float *partial, const void *x, const void *dy, const float *gamma,
+                       int64_t rows, int64_t h, float eps, const Plan &p, int grid, int *status,
+                       cudaStream_t stream) {
+    auto kernel = rms_staged_kernel<BWD, VPT, BF16>;
+    static bool attr_done[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+        if (e != cudaSuccess) return e;
+        attr_done[dev] = true;
+    }
+    kernel<<<grid, kThreads, p.smem, stream>>>(static_cast<uint4 *>(out), partial, static_cast<const uint4 *>(x),
+                                               static_cast<const uint4 *>(dy), gamma, rows,
+                                               static_cast<int>(h / 8), static_cast<float>(h), eps, p.stages, p.T,
+                                               p.G, status);
+    return cudaGetLastError();
+}
+
+template <bool BWD>
+cudaError_t launch_any(void *out, float *partial, const void *x, const void *dy, const float *gamma, int64_t rows,
+                       int64_t h, float eps, bool bf16, const Plan &p, int grid, int *status, cudaStream_t stream) {
+#define PG_RMS_CASE(V)                                                                                       \
+    if (p.vpt == V)                                                                                          \
+        return bf16 ? launch_one<BWD, V, true>(out, partial, x, dy, gamma, rows, h, eps, p, grid, status, stream) \
+                    : launch_one<BWD, V, false>(out, partial, x, dy, gamma, rows, h, eps, p, grid, status, stream);
+    PG_RMS_CASE(1)
+    PG_RMS_CASE(2)
+    PG_RMS_CASE(4)
+    PG_RMS_CASE(8)
+#undef PG_RMS_CASE
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+bool rmsnorm_staged_supported(int64_t h, bool bwd) {
+    if (const char *e = getenv("PEAKGEMM_TUNE_RMS_STAGED"))
+        if (e[0] == '0') return false;
+    return make_plan(h, bwd).ok;
+}
+
+// CTAs the staged kernels launch for this shape, and (backward) the number of dgamma partial rows
+// they write: one per CTA.
+cudaError_t rmsnorm_staged_ctas(int64_t rows, int64_t h, bool bwd, int *ctas, int *partial_rows) {
+    const Plan p = make_plan(h, bwd);
+    if (!p.ok) return cudaErrorInvalidValue;
+    int sms = 0, *status = nullptr;
+    cudaError_t e = device_setup(&sms, &status);
+    if (e != cudaSuccess) return e;
+    *ctas = static_cast<int>(rows < sms ? rows : sms);
+    *partial_rows = *ctas;
+    return cudaSuccess;
+}
+
+cudaError_t rmsnorm_staged_fwd(const RmsFwdArgs &a, cudaStream_t stream) {
+    const Plan p = make_plan(a.h, false);
+    int sms = 0, *status = nullptr, grid = 0, nparts = 0;
+    cudaError_t e = device_setup(&sms, &status);
+    if (e != cudaSuccess) return e;
+    if ((e = rmsnorm_staged_ctas(a.rows, a.h, false, &grid, &nparts)) != cudaSuccess) return e;
+    return launch_any<false>(a.y, nullptr, a.x, nullptr, a.gamma, a.rows, a.h, a.eps, a.bf16, p, grid, status, stream);
+}
+
+cudaError_t rmsnorm_staged_bwd(const RmsBwdArgs &a, cudaStream_t stream) {
+    const Plan p = make_plan(a.h, true);
+    int sms = 0, *status = nullptr, ctas = 0, nparts = 0;
+    cudaError_t e = device_setup(&sms, &status);
+    if (e != cudaSuccess) return e;
+    if ((e = rmsnorm_staged_ctas(a.rows, a.h, true, &ctas, &nparts)) != cudaSuccess) return e;
+    return launch_any<true>(a.dx, static_cast<float *>(a.workspace), a.x, a.dy, a.gamma, a.rows, a.h, a.eps, a.bf16,
+                            p, ctas, status, stream);
+}
+
+cudaError_t rmsnorm_device_status(int *out, cudaStream_t stream) {
+    int sms = 0, *status = nullptr;
+    cudaError_t e = device_setup(&sms, &status);
+    if (e != cudaSuccess) return e;
+    int host = 0;
+    if ((e = cudaMemcpyAsync(&host, status, sizeof(int), cudaMemcpyDeviceToHost, stream)) != cudaSuccess) return e;
+    if ((e = cudaStreamSynchronize(stream)) != cudaSuccess) return e;
+    if (host != 0 && (e = cudaMemsetAsync(status, 0, sizeof(int), stream)) != cudaSuccess) return e;
+    *out = host;
+    return cudaSuccess;
+}
+
+}  // namespace pg

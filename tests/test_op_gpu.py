@@ -74,7 +74,7 @@ def test_rms_norm_ops(cuda):
     torch.cuda.synchronize()
     assert oracle.ulp_distance_16(y.cpu().view(-1, 2048), oracle.rmsnorm_fwd(x, gamma)).max() <= 1
     dx_ref, dg_ref = oracle.rmsnorm_bwd(dy, x, gamma)
-    assert oracle.ulp_distance_16(dx.cpu().view(-1, 2048), dx_ref).max() <= 1
+    assert oracle.within_ulp_or_slack(dx.cpu().view(-1, 2048), dx_ref, oracle.rmsnorm_bwd_dx_slack(dy, x, gamma)).all()
     assert (dg.cpu() - dg_ref).abs().max() <= 1e-3 * dg_ref.abs().max()
 
 
@@ -95,5 +95,5 @@ def test_rms_norm_matches_torch_autograd(cuda):
     PeakGemm.rms_norm_bwd(dx, dg, dyd, xd, gd)
     torch.cuda.synchronize()
     assert oracle.ulp_distance_16(y.cpu(), yt.detach().cpu()).max() <= 1
-    assert oracle.ulp_distance_16(dx.cpu(), xf.grad.cpu()).max() <= 1
+    assert oracle.within_ulp_or_slack(dx.cpu(), xf.grad.cpu(), oracle.rmsnorm_bwd_dx_slack(dy, x, gamma)).all()
     assert (dg - gf.grad).abs().max() <= 1e-3 * gf.grad.abs().max()

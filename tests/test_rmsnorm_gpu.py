@@ -1,7 +1,9 @@
 """GPU parity of the RMSNorm kernels with the fp32 oracle, through the C ABI.
 
 Bounds: y and dx within 1 ulp (of the 16-bit output type) of the fp32 oracle result rounded to that
-type; dgamma within 1e-3 * max|dgamma_ref|.  The reference project has no RMSNorm, so this oracle is
+type — for dx plus the fp32 error bound of its own formula (oracle.rmsnorm_bwd_dx_slack: roundings of the
+cancelling subtraction g - xhat*c and the summation error of c), which only matters where dx cancelled to
+almost nothing; dgamma within 1e-3 * max|dgamma_ref|.  The reference project has no RMSNorm, so this oracle is
 the textbook definition (parity unpinned by the reference).
 """
 import pytest
@@ -18,6 +20,7 @@ BF16, F16 = torch.bfloat16, torch.float16
 def run_fwd(rows, h, dtype, seed=3, eps=1e-6):
     from peakgemm_b200 import capi
 
+    assert capi.device_status() == 0
     x, _, gamma = oracle.rmsnorm_inputs(rows, h, dtype, seed)
     y = helpers.garbage_like((rows, h), dtype, "cuda")
     capi.rmsnorm_fwd(y, x.cuda(), gamma.cuda(), eps)
@@ -39,25 +42,27 @@ def run_bwd(rows, h, dtype, seed=3, eps=1e-6):
     ws = torch.full((ws_bytes // 4,), float("nan"), device="cuda")   # the workspace needs no initialisation
     capi.rmsnorm_bwd(dx, dgamma, dy.cuda(), x.cuda(), gamma.cuda(), ws, eps)
     torch.cuda.synchronize()
+    assert capi.device_status() == 0, "a kernel abandoned a bounded wait"
     dx_ref, dg_ref = oracle.rmsnorm_bwd(dy, x, gamma, eps)
-    d = oracle.ulp_distance_16(dx.cpu(), dx_ref)
-    # dx = rstd * (g - xhat*cm): where the two terms cancel the fp32 result itself carries a few fp32 ulps of
-    # error, which can straddle one more 16-bit rounding boundary only if |dx| is tiny; allow 1 ulp everywhere.
-    assert d.max().item() <= 1, f"dx off by {d.max().item()} ulp"
+    # dx within 1 ulp of the rounded oracle value, or, where g - xhat*c cancels, within the fp32 error bound of
+    # the formula (oracle.rmsnorm_bwd_dx_slack).
+    ok = oracle.within_ulp_or_slack(dx.cpu(), dx_ref, oracle.rmsnorm_bwd_dx_slack(dy, x, gamma, eps))
+    assert ok.all(), f"dx: {(~ok).sum().item()} elements outside 1 ulp + cancellation slack"
     err = (dgamma.cpu() - dg_ref).abs().max().item()
     assert err <= 1e-3 * dg_ref.abs().max().item(), f"dgamma err {err}"
 
 
 @pytest.mark.parametrize("dtype", [BF16, F16])
 @pytest.mark.parametrize("rows,h", [(1, 8), (7, 64), (33, 256), (100, 1000), (257, 4096), (64, 8192),
-                                    (19, 5120), (5, 16384), (3, 24576)])
+                                    (19, 5120), (5, 16384), (3, 24576), (1, 2048), (301, 2048), (1000, 3072)])
 def test_fwd_shapes(cuda, rows, h, dtype):
     run_fwd(rows, h, dtype)
 
 
 @pytest.mark.parametrize("dtype", [BF16, F16])
 @pytest.mark.parametrize("rows,h", [(1, 8), (7, 64), (33, 256), (100, 1000), (257, 4096), (64, 8192),
-                                    (19, 5120), (5, 16384), (3, 24576), (1000, 512)])
+                                    (19, 5120), (5, 16384), (3, 24576), (1000, 512), (1, 2048), (301, 2048),
+                                    (1000, 3072)])
 def test_bwd_shapes(cuda, rows, h, dtype):
     run_bwd(rows, h, dtype)
 
