@@ -36,7 +36,8 @@ enum pg_status {
     PG_ERR_WORKSPACE = 4,      /* caller's workspace is too small                      */
     PG_ERR_CUDA = 5,           /* a CUDA runtime/driver call failed (see pg_last_cuda_error) */
     PG_ERR_DEVICE_TIMEOUT = 6, /* a kernel gave up on a bounded wait (see pg_device_status)  */
-    PG_ERR_NOT_SM100 = 7       /* the current device is not compute capability 10.x    */
+    PG_ERR_NOT_SM100 = 7,      /* the current device is not compute capability 10.x    */
+    PG_ERR_STATIC_SCRATCH = 8  /* shape needs more than PG_STATIC_SCRATCH_BYTES of built-in scratch */
 };
 
 /* Human-readable name of a pg_status value; never NULL. */
@@ -129,6 +130,38 @@ size_t pg_rmsnorm_bwd_workspace_bytes(int64_t rows, int64_t h);
 int pg_rmsnorm_bwd(void *dx, float *dgamma, const void *dy, const void *x,
                    const float *gamma, int64_t rows, int64_t h, float eps,
                    int dtype, void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * RMSNorm backward without any allocation — no counterpart in the reference
+ * project (which has neither RMSNorm nor a scratch-using kernel).
+ *
+ * Same arithmetic, same kernels and bit-identical results as pg_rmsnorm_bwd, but
+ * the caller passes no workspace: the table of fp32 dgamma partial rows lives in
+ * a fixed array inside the library (PG_STATIC_SCRATCH_BYTES per GPU, resident
+ * from the moment the library is loaded on that GPU until the process exits).
+ * Meant for hosts that cannot call cudaMalloc or any allocator where this runs:
+ * plugins invoked inside another framework's stream-ordered region, latency-
+ * critical loops that must not take allocator locks, plain C/Fortran hosts that
+ * only hold raw device pointers.  The call itself makes no cudaMalloc, cudaFree
+ * or other allocating call.
+ *
+ * Limits and rules:
+ *  - the shape must fit: pg_rmsnorm_bwd_workspace_bytes(rows, h) <=
+ *    PG_STATIC_SCRATCH_BYTES (e.g. h <= 8192 on a 148-SM B200); otherwise the
+ *    call does nothing and returns PG_ERR_STATIC_SCRATCH;
+ *  - the first call on each device looks up the array's device address (the
+ *    device must be current); make that first call before starting any stream
+ *    capture;
+ *  - every call on a device shares the one array.  Nothing in it has to start at
+ *    zero (each partial row is fully written before it is read), but two calls
+ *    whose kernels overlap on the GPU — different streams, no ordering between
+ *    them — race on it and corrupt each other's dgamma.  Serialise them, or use
+ *    pg_rmsnorm_bwd with separate workspaces.
+ */
+#define PG_STATIC_SCRATCH_BYTES (160u * 8192u * 4u)
+int pg_rmsnorm_bwd_static(void *dx, float *dgamma, const void *dy, const void *x,
+                          const float *gamma, int64_t rows, int64_t h, float eps,
+                          int dtype, void *stream);
 
 #ifdef __cplusplus
 }

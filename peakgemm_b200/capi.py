@@ -27,7 +27,9 @@ SIGNATURES = {
     "pg_rmsnorm_fwd": (_i, [_p, _p, _p, _i64, _i64, _f, _i, _p]),
     "pg_rmsnorm_bwd_workspace_bytes": (_sz, [_i64, _i64]),
     "pg_rmsnorm_bwd": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _f, _i, _p, _sz, _p]),
+    "pg_rmsnorm_bwd_static": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _f, _i, _p]),
 }
+PG_STATIC_SCRATCH_BYTES = 160 * 8192 * 4
 
 _lib = None
 
@@ -109,3 +111,11 @@ def rmsnorm_bwd(dx, dgamma, dy, x, gamma, workspace, eps: float = 1e-6, stream=N
                                rows, h, eps, dtype_code(x.dtype), workspace.data_ptr(),
                                workspace.numel() * workspace.element_size(), _stream_ptr(stream)),
           "pg_rmsnorm_bwd")
+
+
+def rmsnorm_bwd_static(dx, dgamma, dy, x, gamma, eps: float = 1e-6, stream=None) -> None:
+    """pg_rmsnorm_bwd_static: the backward pass with the library's built-in scratch (no workspace argument)."""
+    rows, h = x.shape
+    check(lib().pg_rmsnorm_bwd_static(dx.data_ptr(), dgamma.data_ptr(), dy.data_ptr(), x.data_ptr(),
+                                      gamma.data_ptr(), rows, h, eps, dtype_code(x.dtype), _stream_ptr(stream)),
+          "pg_rmsnorm_bwd_static")

@@ -45,6 +45,9 @@ const char *pg_status_string(int status) {
         case PG_ERR_CUDA: return "PG_ERR_CUDA: a CUDA call failed (pg_last_cuda_error)";
         case PG_ERR_DEVICE_TIMEOUT: return "PG_ERR_DEVICE_TIMEOUT: a kernel abandoned a bounded wait";
         case PG_ERR_NOT_SM100: return "PG_ERR_NOT_SM100: the current device is not compute capability 10.x";
+        case PG_ERR_STATIC_SCRATCH:
+            return "PG_ERR_STATIC_SCRATCH: this shape needs more scratch than the library's built-in "
+                   "PG_STATIC_SCRATCH_BYTES; use pg_rmsnorm_bwd with a caller workspace";
         default: return "unknown pg_status";
     }
 }
