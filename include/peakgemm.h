@@ -82,13 +82,25 @@ int pg_hgemm(void *c, const void *a, const void *b,
  *   variant 1 = one CTA per 128 x block_n tile   (tcgen05 cta_group::1)
  *   variant 2 = CTA pair per 256 x block_n tile  (tcgen05 cta_group::2)
  *   block_n   = 0 (automatic), 64, 128 or 256
- * Meant for benchmarks and tests; the reference fixes one configuration at
- * compile time (REGISTER_HGEMM_WMMA_M16N8K16_IMPL, hgemm_wmma_impl.h:410).
+ *   max_sms   = 0 (all SMs), or the number of SMs the persistent grid may occupy;
+ *               a caller that overlaps a collective with the GEMM leaves a few
+ *               SMs free for the collective's kernels this way
+ * Meant for benchmarks, tests and the sharded caller; the reference fixes one
+ * configuration at compile time (REGISTER_HGEMM_WMMA_M16N8K16_IMPL,
+ * hgemm_wmma_impl.h:410) and launches one CTA per tile (get_grid, :373-378).
  */
 int pg_hgemm_ex(void *c, const void *a, const void *b,
                 int64_t m, int64_t n, int64_t k,
                 int64_t lda, int64_t ldb, int64_t ldc,
-                int dtype, int variant, int block_n, void *stream);
+                int dtype, int variant, int block_n, int max_sms, void *stream);
+
+/*
+ * The configuration pg_hgemm would choose for this shape on a device with
+ * sm_count SMs: writes variant (1 or 2) and block_n (64, 128, 256).  Pure host
+ * arithmetic, needs no GPU.  (The reference's counterpart is the fixed
+ * instantiation at hgemm_wmma_impl.h:410,421.)
+ */
+int pg_hgemm_config(int64_t m, int64_t n, int64_t k, int sm_count, int *variant, int *block_n);
 
 /*
  * Device-side status word of the kernels on the current device: 0 if no kernel

@@ -22,7 +22,8 @@ SIGNATURES = {
     "pg_last_cuda_error": (_i, []),
     "pg_version": (ctypes.c_char_p, []),
     "pg_hgemm": (_i, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _p]),
-    "pg_hgemm_ex": (_i, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _p]),
+    "pg_hgemm_ex": (_i, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _p]),
+    "pg_hgemm_config": (_i, [_i64, _i64, _i64, _i, ctypes.POINTER(_i), ctypes.POINTER(_i)]),
     "pg_device_status": (_i, [ctypes.POINTER(_i), _p]),
     "pg_rmsnorm_fwd": (_i, [_p, _p, _p, _i64, _i64, _f, _i, _p]),
     "pg_rmsnorm_bwd_workspace_bytes": (_sz, [_i64, _i64]),
@@ -79,14 +80,22 @@ def _stream_ptr(stream=None):
     return ctypes.c_void_p(s.cuda_stream)
 
 
-def hgemm(c, a, b, *, variant: int = 0, block_n: int = 0, ldc: int | None = None, stream=None) -> None:
+def hgemm(c, a, b, *, variant: int = 0, block_n: int = 0, max_sms: int = 0, ldc: int | None = None,
+          stream=None) -> None:
     """C[m,n] = A[m,k] @ B[n,k]^T through pg_hgemm_ex on torch CUDA tensors (2-D, row-major)."""
     m, k = a.shape
     n = b.shape[0]
     st = lib().pg_hgemm_ex(c.data_ptr(), a.data_ptr(), b.data_ptr(), m, n, k, a.stride(0) if m > 1 else k,
                            b.stride(0) if n > 1 else k, ldc if ldc is not None else (c.stride(0) if m > 1 else n),
-                           dtype_code(a.dtype), variant, block_n, _stream_ptr(stream))
+                           dtype_code(a.dtype), variant, block_n, max_sms, _stream_ptr(stream))
     check(st, "pg_hgemm_ex")
+
+
+def hgemm_config(m: int, n: int, k: int, sm_count: int = 148) -> tuple[int, int]:
+    """(variant, block_n) pg_hgemm picks for this shape; host arithmetic only."""
+    v, bn = ctypes.c_int(0), ctypes.c_int(0)
+    check(lib().pg_hgemm_config(m, n, k, sm_count, ctypes.byref(v), ctypes.byref(bn)), "pg_hgemm_config")
+    return v.value, bn.value
 
 
 def device_status(stream=None) -> int:

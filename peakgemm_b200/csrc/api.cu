@@ -57,8 +57,8 @@ int pg_last_cuda_error(void) { return t_last_cuda_error; }
 const char *pg_version(void) { return "0.1"; }
 
 int pg_hgemm_ex(void *c, const void *a, const void *b, int64_t m, int64_t n, int64_t k, int64_t lda,
-                int64_t ldb, int64_t ldc, int dtype, int variant, int block_n, void *stream) {
-    if (m < 0 || n < 0 || k < 0) return PG_ERR_BAD_ARG;
+                int64_t ldb, int64_t ldc, int dtype, int variant, int block_n, int max_sms, void *stream) {
+    if (m < 0 || n < 0 || k < 0 || max_sms < 0) return PG_ERR_BAD_ARG;
     if (dtype != PG_F16 && dtype != PG_BF16) return PG_ERR_BAD_ARG;
     if (variant < 0 || variant > 2) return PG_ERR_BAD_ARG;
     if (block_n != 0 && block_n != 64 && block_n != 128 && block_n != 256) return PG_ERR_BAD_ARG;
@@ -70,13 +70,22 @@ int pg_hgemm_ex(void *c, const void *a, const void *b, int64_t m, int64_t n, int
     if (!aligned16(c) || (k > 0 && (!aligned16(a) || !aligned16(b)))) return PG_ERR_MISALIGNED;
     pg::GemmArgs g{c, a, b, m, n, k, lda, ldb, ldc, dtype == PG_BF16};
     cudaError_t e = cudaSuccess;
-    const int r = pg::hgemm_launch(g, variant, block_n, static_cast<cudaStream_t>(stream), &e);
+    const int r = pg::hgemm_launch(g, variant, block_n, max_sms, static_cast<cudaStream_t>(stream), &e);
     return from_launch(r, e);
 }
 
 int pg_hgemm(void *c, const void *a, const void *b, int64_t m, int64_t n, int64_t k, int64_t lda,
              int64_t ldb, int64_t ldc, int dtype, void *stream) {
-    return pg_hgemm_ex(c, a, b, m, n, k, lda, ldb, ldc, dtype, 0, 0, stream);
+    return pg_hgemm_ex(c, a, b, m, n, k, lda, ldb, ldc, dtype, 0, 0, 0, stream);
+}
+
+int pg_hgemm_config(int64_t m, int64_t n, int64_t k, int sm_count, int *variant, int *block_n) {
+    if (m <= 0 || n <= 0 || k < 0 || sm_count < 2 || !variant || !block_n) return PG_ERR_BAD_ARG;
+    pg::GemmArgs g{nullptr, nullptr, nullptr, m, n, k, k, k, n, true};
+    *variant = 0;
+    *block_n = 0;
+    pg::choose_config(g, sm_count, variant, block_n);
+    return PG_OK;
 }
 
 int pg_device_status(int *device_status, void *stream) {

@@ -489,7 +489,7 @@ cudaError_t device_info(DeviceInfo **out) {
 }
 
 template <int CTA_GROUP, int BN, int STAGES, bool BF16>
-cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, cudaStream_t stream) {
+cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t stream) {
     using C = Cfg<CTA_GROUP, BN, STAGES>;
     auto kernel = hgemm_tcgen05_kernel<CTA_GROUP, BN, STAGES, BF16>;
     static bool attr_done[64] = {};
@@ -510,7 +510,7 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, cudaStream_t stream) 
     const uint64_t m_tiles = (g.m + tile_m - 1) / tile_m;
     const uint64_t n_tiles = (g.n + BN - 1) / BN;
     const uint64_t tiles = m_tiles * n_tiles;
-    uint64_t workers = static_cast<uint64_t>(d.sm_count / CTA_GROUP);
+    uint64_t workers = static_cast<uint64_t>(sms / CTA_GROUP);
     if (tiles < workers) workers = tiles;
 
     cudaLaunchConfig_t cfg = {};
@@ -535,9 +535,9 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, cudaStream_t stream) 
 }
 
 template <int CTA_GROUP, int BN, int STAGES>
-cudaError_t launch_dt(const GemmArgs &g, const DeviceInfo &d, cudaStream_t stream) {
-    return g.bf16 ? launch<CTA_GROUP, BN, STAGES, true>(g, d, stream)
-                  : launch<CTA_GROUP, BN, STAGES, false>(g, d, stream);
+cudaError_t launch_dt(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t stream) {
+    return g.bf16 ? launch<CTA_GROUP, BN, STAGES, true>(g, d, sms, stream)
+                  : launch<CTA_GROUP, BN, STAGES, false>(g, d, sms, stream);
 }
 
 }  // namespace
@@ -568,7 +568,8 @@ void choose_config(const GemmArgs &g, int sm_count, int *variant, int *block_n) 
     *block_n = best_bn;
 }
 
-int hgemm_launch(const GemmArgs &g, int variant, int block_n, cudaStream_t stream, cudaError_t *cuda_err) {
+int hgemm_launch(const GemmArgs &g, int variant, int block_n, int max_sms, cudaStream_t stream,
+                 cudaError_t *cuda_err) {
     DeviceInfo *d = nullptr;
     cudaError_t e = device_info(&d);
     if (e != cudaSuccess) { *cuda_err = e; return kLaunchCuda; }
@@ -580,17 +581,19 @@ int hgemm_launch(const GemmArgs &g, int variant, int block_n, cudaStream_t strea
         if (e != cudaSuccess) { *cuda_err = e; return kLaunchCuda; }
         return kLaunchOk;
     }
-    choose_config(g, d->sm_count, &variant, &block_n);
+    int sms = d->sm_count;
+    if (max_sms > 0 && max_sms < sms) sms = max_sms < 2 ? 2 : max_sms;
+    choose_config(g, sms, &variant, &block_n);
 
     if (variant == 1) {
-        if (block_n == 256) e = launch_dt<1, 256, 4>(g, *d, stream);
-        else if (block_n == 128) e = launch_dt<1, 128, 6>(g, *d, stream);
-        else if (block_n == 64) e = launch_dt<1, 64, 8>(g, *d, stream);
+        if (block_n == 256) e = launch_dt<1, 256, 4>(g, *d, sms, stream);
+        else if (block_n == 128) e = launch_dt<1, 128, 6>(g, *d, sms, stream);
+        else if (block_n == 64) e = launch_dt<1, 64, 8>(g, *d, sms, stream);
         else return kLaunchBadConfig;
     } else if (variant == 2) {
-        if (block_n == 256) e = launch_dt<2, 256, 6>(g, *d, stream);
-        else if (block_n == 128) e = launch_dt<2, 128, 8>(g, *d, stream);
-        else if (block_n == 64) e = launch_dt<2, 64, 8>(g, *d, stream);
+        if (block_n == 256) e = launch_dt<2, 256, 6>(g, *d, sms, stream);
+        else if (block_n == 128) e = launch_dt<2, 128, 8>(g, *d, sms, stream);
+        else if (block_n == 64) e = launch_dt<2, 64, 8>(g, *d, sms, stream);
         else return kLaunchBadConfig;
     } else {
         return kLaunchBadConfig;

@@ -17,7 +17,9 @@ struct GemmArgs {
 enum LaunchResult { kLaunchOk = 0, kLaunchCuda = 1, kLaunchNotSm100 = 2, kLaunchBadConfig = 3 };
 
 // variant: 0 auto, 1 = one CTA per tile, 2 = CTA pair per tile; block_n: 0 auto, 64, 128, 256.
-int hgemm_launch(const GemmArgs &g, int variant, int block_n, cudaStream_t stream, cudaError_t *cuda_err);
+// max_sms: 0 = all SMs, else an upper bound on the SMs the persistent grid occupies.
+int hgemm_launch(const GemmArgs &g, int variant, int block_n, int max_sms, cudaStream_t stream,
+                 cudaError_t *cuda_err);
 
 // Resolves variant/block_n == 0 to concrete values for a device with sm_count SMs.
 void choose_config(const GemmArgs &g, int sm_count, int *variant, int *block_n);

@@ -1,0 +1,123 @@
+"""Column-sharded GEMM across the GPUs of one node (one process per GPU, torch.distributed).
+
+The reference project has no multi-GPU code.  The layout here follows from its data format: B is
+stored [n, k] (PeakGemm/__init__.py:27-31), so rank r owns a CONTIGUOUS slab of B rows
+[start_r, stop_r) and computes the column block C[:, start_r:stop_r] from a replicated A.  There is no
+reduction across ranks (k is not split), so the GEMMs need no collective at all; an all-gather over
+NCCL / NVLink runs only when the caller asks for a replicated C.
+
+Layouts of a gathered C:
+  "shard_major"  [world, m, n_local]: rank r's block is out[r]; what the all-gather produces natively.
+  "row_major"    [m, n]: the reference's layout; costs one more device copy (a strided write per block).
+
+With bands > 1 the rows of A are processed in bands: while NCCL gathers band i, the GEMM of band i+1 runs
+(leave the collective a few SMs with max_sms).  The band buffers are gathered in place.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+def column_shard(n: int, world: int, rank: int, multiple: int = 8) -> tuple[int, int]:
+    """Rows [start, stop) of the stored B[n, k] (= columns of C) that `rank` owns.
+
+    Blocks are contiguous, equal (ceil(n / world) rounded up to `multiple`) except possibly the last
+    non-empty one; their union is [0, n) and every start is a multiple of `multiple` (16-byte alignment
+    of a bf16/fp16 column block inside a full-width C).
+    """
+    if n < 0 or world < 1 or not (0 <= rank < world):
+        raise ValueError("bad shard request")
+    per = -(-n // world)
+    per = -(-per // multiple) * multiple
+    start = min(n, rank * per)
+    return start, min(n, start + per)
+
+
+def row_bands(m: int, bands: int, multiple: int = 256) -> list[tuple[int, int]]:
+    """Splits [0, m) into at most `bands` contiguous row bands whose sizes are multiples of `multiple`
+    (the pair kernel's tile height) except the last."""
+    bands = max(1, bands)
+    per = -(-m // bands)
+    per = max(multiple, -(-per // multiple) * multiple)
+    out, r = [], 0
+    while r < m:
+        out.append((r, min(m, r + per)))
+        r += per
+    return out or [(0, 0)]
+
+
+def _default_gemm(c, a, b, ldc, max_sms):
+    from . import capi   # the CUDA path; there is no fallback
+
+    capi.hgemm(c, a, b, ldc=ldc, max_sms=max_sms)
+
+
+class ShardedGemm:
+    """C = A @ B^T with B sharded by rows (columns of C) over the ranks of `group`.
+
+    `gemm(c, a, b, ldc, max_sms)` computes one block in place; it defaults to the sm_100a kernel through the
+    C ABI.  Tests on CPU ranks (gloo) pass the oracle here to exercise the sharding and gather logic.
+    """
+
+    def __init__(self, n: int, group=None, gemm=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.n = n
+        self.start, self.stop = column_shard(n, self.world, self.rank)
+        self.gemm = gemm or _default_gemm
+
+    @property
+    def n_local(self) -> int:
+        return self.stop - self.start
+
+    def local(self, a: torch.Tensor, b_shard: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """This rank's column block, contiguous [m, n_local].  No communication."""
+        m = a.shape[0]
+        assert b_shard.shape[0] == self.n_local and b_shard.shape[1] == a.shape[1]
+        if out is None:
+            out = torch.empty(m, self.n_local, dtype=a.dtype, device=a.device)
+        if self.n_local:
+            self.gemm(out, a, b_shard, self.n_local, 0)
+        return out
+
+    def local_into_full(self, c_full: torch.Tensor, a: torch.Tensor, b_shard: torch.Tensor) -> torch.Tensor:
+        """Writes this rank's block into columns [start, stop) of a full-width row-major C[m, n] (ldc = n)."""
+        assert c_full.shape == (a.shape[0], self.n) and c_full.is_contiguous()
+        if self.n_local:
+            self.gemm(c_full[:, self.start:self.stop], a, b_shard, self.n, 0)
+        return c_full
+
+    def gathered(self, a: torch.Tensor, b_shard: torch.Tensor, layout: str = "row_major", bands: int = 1,
+                 max_sms: int = 0) -> torch.Tensor:
+        """Replicated C on every rank: local GEMM + all-gather of the column blocks (band-pipelined)."""
+        if layout not in ("row_major", "shard_major"):
+            raise ValueError(layout)
+        m, w, nl = a.shape[0], self.world, self.n_local
+        if w == 1:
+            c = self.local(a, b_shard)
+            return c if layout == "row_major" else c.view(1, m, nl)
+        if self.n != nl * w:
+            raise ValueError("gathered() needs equal shards: n must be a multiple of 8 * world")
+        spans = row_bands(m, bands)
+        # flat buffer: band after band, each band [world, rows_in_band, n_local] contiguous
+        flat = torch.empty(w * m * nl, dtype=a.dtype, device=a.device)
+        works, views = [], []
+        for (r0, r1) in spans:
+            band = flat[w * r0 * nl: w * r1 * nl].view(w, r1 - r0, nl)
+            self.gemm(band[self.rank], a[r0:r1], b_shard, nl, max_sms if len(spans) > 1 else 0)
+            works.append(dist.all_gather_into_tensor(band.view(-1), band[self.rank].reshape(-1), group=self.group,
+                                                     async_op=True))
+            views.append(band)
+        for wk in works:
+            wk.wait()
+        if layout == "shard_major":
+            if len(spans) == 1:
+                return views[0]
+            return torch.cat(views, dim=1)
+        out = torch.empty(m, self.n, dtype=a.dtype, device=a.device)
+        out3 = out.view(m, w, nl)
+        for (r0, r1), band in zip(spans, views):
+            out3[r0:r1].copy_(band.transpose(0, 1))      # block r -> columns [r*nl, (r+1)*nl)
+        return out

@@ -1,0 +1,138 @@
+"""CPU: the C-ABI library loads and exports every symbol include/peakgemm.h declares; calls that must
+return before touching CUDA do so with the right status; the torch operators are registered with the
+reference's schema.  No compute call is made here."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(REPO, "include", "peakgemm.h")
+
+
+def declared_functions():
+    src = open(HEADER).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\b(pg_[a-z0-9_]+)\s*\(", src)))
+
+
+def test_header_declares_the_expected_surface():
+    names = declared_functions()
+    for must in ("pg_hgemm", "pg_hgemm_ex", "pg_hgemm_config", "pg_rmsnorm_fwd", "pg_rmsnorm_bwd",
+                 "pg_rmsnorm_bwd_workspace_bytes", "pg_rmsnorm_bwd_static", "pg_device_status",
+                 "pg_status_string", "pg_last_cuda_error", "pg_version"):
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol():
+    from peakgemm_b200 import capi
+
+    lib = ctypes.CDLL(capi.DEVICE_LIB_PATH)
+    for name in declared_functions():
+        assert hasattr(lib, name), f"{name} declared in include/peakgemm.h but not exported"
+    assert sorted(capi.SIGNATURES) == declared_functions()     # the ctypes binding covers the same set
+
+
+def test_status_strings():
+    from peakgemm_b200 import capi
+
+    L = capi.lib()
+    assert L.pg_status_string(0) == b"PG_OK"
+    seen = {L.pg_status_string(i) for i in range(0, 9)}
+    assert len(seen) == 9 and all(s.startswith(b"PG_") for s in seen)
+    assert L.pg_status_string(99) == b"unknown pg_status"
+    assert L.pg_version() == b"0.1"
+
+
+def test_argument_checks_return_before_any_cuda_call():
+    from peakgemm_b200 import capi
+
+    L = capi.lib()
+    p = 4096                                     # a fake, aligned, never dereferenced address
+    ex = lambda *a: L.pg_hgemm_ex(*a)            # noqa: E731
+    assert L.pg_hgemm(p, p, p, 0, 64, 64, 64, 64, 64, 1, None) == 0           # m == 0: no-op
+    assert L.pg_hgemm(p, p, p, 64, 0, 64, 64, 64, 0, 1, None) == 0            # n == 0: no-op
+    assert L.pg_hgemm(p, p, p, -1, 64, 64, 64, 64, 64, 1, None) == 1
+    assert L.pg_hgemm(p, p, p, 64, 64, 64, 64, 64, 64, 5, None) == 1          # dtype
+    assert L.pg_hgemm(None, p, p, 64, 64, 64, 64, 64, 64, 1, None) == 1       # null C
+    assert L.pg_hgemm(p, p, p, 64, 64, 64, 32, 64, 64, 1, None) == 1          # lda < k
+    assert L.pg_hgemm(p, p, p, 64, 12, 64, 64, 64, 12, 1, None) == 3          # n % 8
+    assert L.pg_hgemm(p, p, p, 64, 64, 20, 20, 20, 64, 1, None) == 3          # k % 8
+    assert L.pg_hgemm(p, p, p, 64, 64, 64, 64, 64, 68, 1, None) == 3          # ldc % 8
+    assert L.pg_hgemm(p, p, p, 2 ** 31, 64, 64, 64, 64, 64, 1, None) == 3     # size limit
+    assert L.pg_hgemm(p + 2, p, p, 64, 64, 64, 64, 64, 64, 1, None) == 2      # misaligned
+    assert ex(p, p, p, 64, 64, 64, 64, 64, 64, 1, 3, 0, 0, None) == 1         # variant
+    assert ex(p, p, p, 64, 64, 64, 64, 64, 64, 1, 1, 100, 0, None) == 1       # block_n
+    assert ex(p, p, p, 64, 64, 64, 64, 64, 64, 1, 1, 64, -1, None) == 1       # max_sms
+    assert L.pg_rmsnorm_fwd(p, p, p, 0, 64, 1e-6, 1, None) == 0               # rows == 0
+    assert L.pg_rmsnorm_fwd(p, p, p, 4, 60, 1e-6, 1, None) == 3               # h % 8
+    assert L.pg_rmsnorm_fwd(p, p, p, 4, 0, 1e-6, 1, None) == 1
+    assert L.pg_rmsnorm_fwd(p, None, p, 4, 64, 1e-6, 1, None) == 1
+    assert L.pg_rmsnorm_bwd(p, None, p, p, p, 4, 64, 1e-6, 1, p, 1 << 20, None) == 1
+    assert L.pg_rmsnorm_bwd(p, p, p, p, p, 4, 1 << 20, 1e-6, 1, p, 1 << 20, None) == 3    # h over the limit
+    assert L.pg_rmsnorm_bwd_static(p, p, p, p, p, 4, 60, 1e-6, 1, None) == 3
+    assert L.pg_rmsnorm_bwd_static(p, p, p, p, p, 4, 64, 1e-6, 9, None) == 1
+    assert L.pg_device_status(None, None) == 1
+    assert capi.lib().pg_rmsnorm_bwd_workspace_bytes(0, 64) == 0
+
+
+def test_config_choice_is_host_arithmetic():
+    from peakgemm_b200 import capi
+
+    assert capi.hgemm_config(8192, 8192, 8192) == (2, 256)        # headline shape: CTA pairs, 256-wide tiles
+    assert capi.hgemm_config(16384, 16384, 16384) == (2, 256)
+    v, bn = capi.hgemm_config(16, 4096, 4096)
+    assert v == 1 and bn == 64                                    # one tile row: no pair, most CTAs
+    v, bn = capi.hgemm_config(128, 128256, 4096)
+    assert v == 1                                                 # m <= 128: a pair would idle half its rows
+    for m in (1, 100, 129, 1000, 5000):
+        for n in (8, 512, 4096, 14336):
+            v, bn = capi.hgemm_config(m, n, 4096)
+            assert v in (1, 2) and bn in (64, 128, 256)
+            assert not (v == 2 and m <= 128)
+    assert capi.lib().pg_hgemm_config(0, 8, 8, 148, None, None) == 1
+
+
+def test_torch_operator_schemas_match_the_reference():
+    import peakgemm_b200  # noqa: F401
+
+    s = str(torch.ops.PeakGemm.gemm_peak.default._schema)
+    # src/register.cpp:5 of the reference, verbatim
+    assert s == "PeakGemm::gemm_peak(Tensor c, Tensor a, Tensor b, SymInt m, SymInt n, SymInt k) -> ()"
+    assert str(torch.ops.PeakGemm.rms_norm_fwd.default._schema) == \
+        "PeakGemm::rms_norm_fwd(Tensor y, Tensor x, Tensor gamma, float eps) -> ()"
+    assert str(torch.ops.PeakGemm.rms_norm_bwd.default._schema) == \
+        "PeakGemm::rms_norm_bwd(Tensor dx, Tensor dgamma, Tensor dy, Tensor x, Tensor gamma, float eps) -> ()"
+
+
+def test_python_surface_mirrors_the_reference_wrapper():
+    """Same shape plumbing and asserts as PeakGemm/__init__.py:21-34; no CPU fallback."""
+    import PeakGemm
+    import peakgemm_b200
+
+    assert PeakGemm.gemm_peak is peakgemm_b200.gemm_peak
+    a = torch.zeros(2, 3, 16, dtype=torch.bfloat16)
+    b = torch.zeros(8, 16, dtype=torch.bfloat16)
+    with pytest.raises(AssertionError):
+        PeakGemm.gemm_peak(torch.zeros(2, 3, 8, dtype=torch.bfloat16), a, torch.zeros(8, 24, dtype=torch.bfloat16))
+    with pytest.raises(AssertionError):
+        PeakGemm.gemm_peak(torch.zeros(5, 8, dtype=torch.bfloat16), a, b)          # rows of c != rows of a
+    with pytest.raises(AssertionError):
+        PeakGemm.gemm_peak(torch.zeros(6, 8, dtype=torch.int32), a.int(), b.int())   # dtype assert
+    with pytest.raises(RuntimeError, match="CUDA"):
+        PeakGemm.gemm_peak(torch.zeros(2, 3, 8, dtype=torch.bfloat16), a, b)       # CPU tensors: refused
+    with pytest.raises(RuntimeError, match="CUDA"):
+        PeakGemm.rms_norm_fwd(torch.zeros(4, 16, dtype=torch.bfloat16), torch.zeros(4, 16, dtype=torch.bfloat16),
+                              torch.ones(16))
+
+
+def test_product_code_never_imports_the_oracle():
+    """The oracle is test infrastructure: nothing under peakgemm_b200/ or PeakGemm/ may reference it."""
+    for root in ("peakgemm_b200", "PeakGemm"):
+        for dirpath, _, files in os.walk(os.path.join(REPO, root)):
+            for f in files:
+                if f.endswith((".py", ".cu", ".cuh", ".h", ".cpp")):
+                    text = open(os.path.join(dirpath, f)).read()
+                    assert "import oracle" not in text and "from oracle" not in text and "oracle/" not in text, f

@@ -115,7 +115,7 @@ def test_argument_errors(cuda):
     assert L.pg_hgemm(None, p, p, 128, 64, 64, 64, 64, 64, 1, None) == 1   # null
     assert L.pg_hgemm(p, p, p, -1, 64, 64, 64, 64, 64, 1, None) == 1
     assert L.pg_hgemm(p, p, p, 128, 64, 64, 64, 64, 64, 7, None) == 1      # dtype
-    assert L.pg_hgemm_ex(p, p, p, 128, 64, 64, 64, 64, 64, 1, 1, 96, None) == 1  # block_n
+    assert L.pg_hgemm_ex(p, p, p, 128, 64, 64, 64, 64, 64, 1, 1, 96, 0, None) == 1  # block_n
 
 
 # ---- BASELINE configurations
