@@ -113,10 +113,20 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def use_all_host_threads() -> int:
+    """torchrun exports OMP_NUM_THREADS=1; the CPU legs are meant to use every core this process may run on."""
+    import torch
+
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
 def cpu_gemm_baseline(target_seconds: float = 12.0) -> dict:
     """torch CPU fp32 matmul on a row band of the 8192^3 problem (A band [rows, k] x full B)."""
     import torch
 
+    use_all_host_threads()
     torch.manual_seed(1)
     b = (torch.rand(N, K) * 2 - 1).to(torch.bfloat16).float()
     rows = 256
@@ -148,6 +158,7 @@ def run_reference_arm(args) -> None:
         return
     import torch
 
+    use_all_host_threads()
     torch.manual_seed(1)
     b = (torch.rand(N, K) * 2 - 1).to(torch.bfloat16).float()
     rows = 1024

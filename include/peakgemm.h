@@ -81,6 +81,10 @@ int pg_hgemm(void *c, const void *a, const void *b,
  *   variant 0 = automatic (what pg_hgemm uses)
  *   variant 1 = one CTA per 128 x block_n tile   (tcgen05 cta_group::1)
  *   variant 2 = CTA pair per 256 x block_n tile  (tcgen05 cta_group::2)
+ *   variant 3 = cluster split-K: a cluster of 2, 4 or 8 CTAs shares one 128 x block_n
+ *               tile (block_n 64 or 128), each CTA a slice of k; the partial sums are
+ *               combined through distributed shared memory, no global scratch.
+ *               PG_ERR_BAD_ARG if the shape admits no split (k < 256, or too many tiles)
  *   block_n   = 0 (automatic), 64, 128 or 256
  *   max_sms   = 0 (all SMs), or the number of SMs the persistent grid may occupy;
  *               a caller that overlaps a collective with the GEMM leaves a few

@@ -337,6 +337,11 @@ Plan make_plan(int64_t h, bool bwd) {
     int T = static_cast<int>((h8 / 4 + 31) / 32 * 32);
     if (T < 32) T = 32;
     if (T > 256) T = 256;
+    // Benchmark override, read once: PEAKGEMM_TUNE_RMS_T = threads per consumer group (32..256).
+    // Measured on [32768, H] bf16: T=128 is best at H=4096 (T=64: -8 % fwd, -40 % bwd; T=256: -15 %),
+    // T=256 at H=8192 (T=128: -18 % fwd, -40 % bwd).
+    static const int env_t = getenv("PEAKGEMM_TUNE_RMS_T") ? atoi(getenv("PEAKGEMM_TUNE_RMS_T")) : 0;
+    if (env_t >= 32 && env_t <= 256 && env_t % 32 == 0 && (h8 + env_t - 1) / env_t <= 8) T = env_t;
     const int need = static_cast<int>((h8 + T - 1) / T);
     p.vpt = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
     p.T = T;
@@ -411,8 +416,9 @@ cudaError_t launch_any(void *out, float *partial, const void *x, const void *dy,
 }  // namespace
 
 bool rmsnorm_staged_supported(int64_t h, bool bwd) {
-    if (const char *e = getenv("PEAKGEMM_TUNE_RMS_STAGED"))
-        if (e[0] == '0') return false;
+    // Benchmark override, read once: PEAKGEMM_TUNE_RMS_STAGED=0 falls back to the register-resident kernels.
+    static const bool disabled = getenv("PEAKGEMM_TUNE_RMS_STAGED") && getenv("PEAKGEMM_TUNE_RMS_STAGED")[0] == '0';
+    if (disabled) return false;
     return make_plan(h, bwd).ok;
 }
 

@@ -56,6 +56,42 @@ def test_pair_variants(cuda, block_n, dtype):
     run_case(512, 768, 1024, dtype, 2, block_n, seed=1)
 
 
+# ---- cluster split-K (variant 3): 2, 4 or 8 CTAs share a tile and combine partial sums through
+# distributed shared memory.  The shapes steer the planner to every cluster size and slice width.
+@pytest.mark.parametrize("dtype", [BF16, F16])
+@pytest.mark.parametrize("m,n,k,block_n", [
+    (64, 128, 2048, 64),      # 2 tiles  -> S=8, 8 columns per CTA
+    (64, 128, 2048, 128),     # 1 tile   -> S=8, 16 columns per CTA
+    (128, 1024, 1024, 128),   # 8 tiles  -> S=8
+    (16, 4096, 4096, 0),      # BASELINE config 3 shape: 32 tiles of 128 -> S=4
+    (128, 4096, 1024, 64),    # 64 tiles -> S=2
+    (100, 520, 1000, 0),      # tails in m, n and k
+    (64, 2048, 576, 128),     # 9 k-blocks over S=4: the last CTA's slice is empty
+    (200, 264, 8192, 64),     # two tile rows
+])
+def test_split_k_cluster(cuda, m, n, k, block_n, dtype):
+    run_case(m, n, k, dtype, 3, block_n, seed=6)
+
+
+def test_split_k_is_deterministic_and_refuses_unsplittable_shapes(cuda):
+    from peakgemm_b200 import capi
+
+    a, b = oracle.gemm_inputs_uniform(128, 4096, 14336, BF16, 7)
+    ad, bd = a.cuda(), b.cuda()
+    outs = []
+    for _ in range(3):
+        c = torch.empty(128, 4096, dtype=BF16, device="cuda")
+        capi.hgemm(c, ad, bd, variant=3)
+        outs.append(c)
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    helpers.check_gemm(outs[0], a, b, exact_rows=False)
+    p = ad.data_ptr()
+    # k too short to split, and a shape with more tiles than SMs
+    assert capi.lib().pg_hgemm_ex(p, p, p, 128, 64, 64, 64, 64, 64, 1, 3, 0, 0, None) == 1
+    assert capi.lib().pg_hgemm_ex(p, p, p, 8192, 8192, 8192, 8192, 8192, 8192, 1, 3, 0, 0, None) == 1
+
+
 # ---- persistence: more tiles than CTAs, several tiles per CTA, both accumulators reused
 @pytest.mark.parametrize("variant,block_n", [(1, 64), (1, 256), (2, 64), (2, 256)])
 def test_many_tiles_per_cta(cuda, variant, block_n):
