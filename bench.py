@@ -226,6 +226,117 @@ def rmsnorm_numbers(peaks: dict, steps: int, warmup: int, rows: int = 32768) -> 
     return out
 
 
+def shape_sweep(peaks: dict) -> list:
+    """BASELINE configs 2 and 3: every shape, ours (automatic configuration) against cuBLAS on the same GPU.
+
+    Throughput timing as the reference's Python benchmark does it (test/test_gemm.py:62-96): several
+    independent (B, C) sets are rotated through back-to-back launches, enough of them (>= 256 MB of B) that a
+    weight matrix is never found in the 126 MB L2 from its previous use; CUDA events around the whole loop.
+    Roofline time = max(2mnk / measured bf16 peak, 2(mk+nk+mn) / measured HBM peak)."""
+    import torch
+
+    from peakgemm_b200 import capi
+
+    shapes = [("config2", s, s, s, dt) for s in (2048, 4096, 8192, 16384) for dt in (torch.float16, torch.bfloat16)]
+    shapes += [("config3", m, n, k, torch.bfloat16) for m in (16, 128, 1024, 4096)
+               for (n, k) in ((4096, 4096), (14336, 4096), (4096, 14336), (128256, 4096))]
+    rows = []
+    g = torch.Generator(device="cuda").manual_seed(2)
+    for tag, m, n, k, dt in shapes:
+        nbuf = max(1, min(16, -(-(256 << 20) // (2 * n * k))))
+        if tag == "config2":
+            a = (torch.rand(m, k, device="cuda", generator=g) * 2 - 1).to(dt)
+            bs = [(torch.rand(n, k, device="cuda", generator=g) * 2 - 1).to(dt) for _ in range(nbuf)]
+        else:
+            a = torch.randn(m, k, device="cuda", generator=g).to(dt)
+            bs = [(0.02 * torch.randn(n, k, device="cuda", generator=g)).to(dt) for _ in range(nbuf)]
+        cs = [torch.empty(m, n, dtype=dt, device="cuda") for _ in range(nbuf)]
+        iters = max(nbuf, 32 if m * n * k < 2 ** 38 else 8)
+
+        def loop(fn):
+            for i in range(min(iters, 4)):
+                fn(i % nbuf)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(iters):
+                fn(i % nbuf)
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / iters
+
+        t_o = min(loop(lambda i: capi.hgemm(cs[i], a, bs[i])) for _ in range(3))
+        t_c = min(loop(lambda i: torch.matmul(a, bs[i].t(), out=cs[i])) for _ in range(3))
+        fl, by = 2.0 * m * n * k, 2.0 * (m * k + n * k + m * n)
+        t_roof = max(fl / (peaks["bf16_tflops"] * 1e12), by / (peaks["hbm_gbs"] * 1e9)) * 1e3
+        rows.append({"config": tag, "dtype": str(dt)[6:], "m": m, "n": n, "k": k, "weight_sets": nbuf,
+                     "ours_us": t_o * 1e3, "cublas_us": t_c * 1e3, "ours_tflops": fl / t_o / 1e9,
+                     "ours_gbs": by / t_o / 1e6, "roofline_us": t_roof * 1e3, "frac_of_roofline": t_roof / t_o,
+                     "speed_vs_cublas": t_c / t_o})
+        del a, bs, cs
+    assert capi.device_status() == 0
+    return rows
+
+
+def config5(args) -> None:
+    """BASELINE config 5: m = n = 32768, k = 16384 bf16, B column-sharded over the ranks (strong scaling),
+    timed without a gather, with the all-gather (native shard-major result) and with the copy to row-major."""
+    import torch
+    import torch.distributed as dist
+
+    from peakgemm_b200 import capi
+    from peakgemm_b200.dist import ShardedGemm
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    m = n = 32768
+    k = 16384
+    sg = ShardedGemm(n)
+    g = torch.Generator(device="cuda").manual_seed(4)
+    a = (torch.rand(m, k, device="cuda", generator=g) * 2 - 1).to(torch.bfloat16)
+    g.manual_seed(400 + rank)
+    b = (torch.rand(sg.n_local, k, device="cuda", generator=g) * 2 - 1).to(torch.bfloat16)
+    out = torch.empty(m, sg.n_local, dtype=torch.bfloat16, device="cuda")
+
+    def timed(fn, steps):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / steps], device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    res = {"n_gpus": world, "m": m, "n": n, "k": k, "flop": 2.0 * m * n * k}
+    res["no_gather_ms"] = timed(lambda: sg.local(a, b, out=out), args.steps)
+    if world > 1:
+        for bands, max_sms in ((1, 0), (4, 0), (4, 140), (8, 132)):
+            key = f"gather_shard_major_bands{bands}_sms{max_sms}_ms"
+            res[key] = timed(lambda: sg.gathered(a, b, layout="shard_major", bands=bands, max_sms=max_sms),
+                             max(2, args.steps // 2))
+        res["gather_row_major_bands4_ms"] = timed(lambda: sg.gathered(a, b, layout="row_major", bands=4, max_sms=140),
+                                                  max(2, args.steps // 2))
+    res["tflops_no_gather"] = res["flop"] / (res["no_gather_ms"] * 1e-3) / 1e12
+    assert capi.device_status() == 0
+    if rank == 0:
+        print(json.dumps({"config5": res}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -237,6 +348,11 @@ def main() -> None:
     ap.add_argument("--no-extras", action="store_true", help="skip comparators, RMSNorm, e2e and CPU legs")
     ap.add_argument("--size", type=int, default=8192,
                     help="m=n=k of the GEMM; anything but 8192 is a profiling case, not the headline workload")
+    ap.add_argument("--config5", action="store_true",
+                    help="BASELINE config 5 (32768 x 32768 x 16384 sharded over the ranks, with and without the "
+                         "all-gather); prints one JSON object and exits")
+    ap.add_argument("--sweep", action="store_true",
+                    help="BASELINE configs 2 and 3 (every shape) against cuBLAS; prints one JSON object and exits")
     ap.add_argument("--only-rmsnorm", type=int, default=0, metavar="ROWS",
                     help="profiling case: run only the RMSNorm kernels on [ROWS, 4096] and [ROWS, 8192] and exit")
     args = ap.parse_args()
@@ -248,6 +364,9 @@ def main() -> None:
 
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.config5:
+        config5(args)
         return
 
     import torch
@@ -264,6 +383,9 @@ def main() -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     peaks = measured_peaks()
+    if args.sweep:
+        print(json.dumps({"sweep": shape_sweep(peaks), "peaks": {k: v for k, v in peaks.items() if not isinstance(v, dict)}}))
+        return
     if args.only_rmsnorm:
         print(json.dumps({"profiling_case": "rmsnorm", "rows": args.only_rmsnorm,
                           "rmsnorm": rmsnorm_numbers(peaks, args.steps, args.warmup, rows=args.only_rmsnorm)}))

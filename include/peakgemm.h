@@ -85,6 +85,10 @@ int pg_hgemm(void *c, const void *a, const void *b,
  *               tile (block_n 64 or 128), each CTA a slice of k; the partial sums are
  *               combined through distributed shared memory, no global scratch.
  *               PG_ERR_BAD_ARG if the shape admits no split (k < 256, or too many tiles)
+ *   variant 4 = skinny kernel for m <= 64 (weight streaming): the weights take the
+ *               128-row side of the MMA, the tokens its 16/32/64-wide side, 8-12 TMA
+ *               stages deep, optional cluster split-K as in variant 3; block_n ignored.
+ *               PG_ERR_BAD_ARG if m > 64
  *   block_n   = 0 (automatic), 64, 128 or 256
  *   max_sms   = 0 (all SMs), or the number of SMs the persistent grid may occupy;
  *               a caller that overlaps a collective with the GEMM leaves a few

@@ -628,6 +628,197 @@ hgemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     }
 }
 
+// ----------------------------------------------------------------- skinny ----
+//
+// m <= 64 (a handful of tokens against a weight matrix): pure weight streaming, HBM-bound.  The roles
+// of the operands are swapped so that no shared memory or bandwidth is spent on padding rows: the
+// WEIGHTS B[n,k] feed the 128-row side of the MMA, the tokens A[m,k] its narrow side (N = TOK = 16, 32
+// or 64 >= m), and tensor memory holds the TRANSPOSED tile D[n_local, m].  A stage is 16 KiB of
+// weights + TOK*128 bytes of tokens, so 8-12 stages (up to 200 KiB) of weights are in flight per SM.
+// One CTA per 128 weight rows (not persistent); with a cluster of S CTAs each takes a slice of k and
+// the partial tiles are combined through distributed shared memory: CTA r owns 128/S of the tile's
+// rows, every other CTA writes its partial values for those rows into r's receive buffer, one cluster
+// barrier, then r sums in rank order (deterministic) and stores.  S == 1: no exchange.
+template <int TOK, int STAGES>
+struct SnCfg {
+    static constexpr uint32_t kWBytes = kBM * kBK * 2;              // weights tile, 16 KiB
+    static constexpr uint32_t kTBytes = TOK * kBK * 2;              // token tile
+    static constexpr uint32_t kStageBytes = kWBytes + kTBytes;
+    static constexpr uint32_t kTmemCols = TOK < 32 ? 32 : TOK;
+    static constexpr uint32_t kOffW = 0;
+    static constexpr uint32_t kOffT = kOffW + STAGES * kWBytes;
+    static constexpr uint32_t kOffRecv = kOffT + STAGES * kTBytes;  // [S slots][128/S rows][TOK] fp32 = 128*TOK*4
+    static constexpr uint32_t kOffBar = kOffRecv + kBM * TOK * 4;
+    static constexpr uint32_t kNumBars = 2 * STAGES + 1;
+    static constexpr uint32_t kOffMisc = kOffBar + kNumBars * 8;
+    static constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;
+    static_assert(kSmemBytes <= 232448, "exceeds 227 KiB of shared memory");
+    static_assert(TOK == 16 || TOK == 32 || TOK == 64, "token tile");
+};
+
+template <int TOK, int STAGES, bool BF16>
+__global__ void __launch_bounds__(kThreads, 1)
+hgemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_constant__ CUtensorMap tm_w,
+                    uint16_t *__restrict__ c, uint32_t ldc, uint32_t M, uint32_t N, uint32_t K, int *status) {
+    using C = SnCfg<TOK, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+    const uint32_t warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t S = cluster_nctarank();
+    const uint32_t rank = cluster_ctarank();
+    const uint32_t rows_per = kBM / S;                 // tile rows (weight rows) each CTA finally owns: 128 .. 16
+
+    const uint32_t bar_full = smem_base + C::kOffBar;
+    const uint32_t bar_empty = bar_full + STAGES * 8;
+    const uint32_t bar_acc_full = bar_empty + STAGES * 8;
+    const uint32_t tmem_slot = smem_base + C::kOffMisc;
+    volatile uint32_t *tmem_slot_gen = reinterpret_cast<volatile uint32_t *>(smem_gen + C::kOffMisc);
+    volatile uint32_t *abort_flag = tmem_slot_gen + 1;
+    const WaitCtx ctx{abort_flag, status};
+
+    const uint32_t ni = blockIdx.x / S;               // which 128 weight rows
+    const uint32_t k_blocks = (K + kBK - 1) / kBK;
+    const uint32_t per = (k_blocks + S - 1) / S;
+    const uint32_t kb0 = min(k_blocks, rank * per), kb1 = min(k_blocks, kb0 + per);
+    const bool has_k = kb1 > kb0;
+
+    if (warp == 0 && lane == 0) {
+        for (uint32_t s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full + s * 8, 1);
+            mbar_init(bar_empty + s * 8, 1);
+        }
+        mbar_init(bar_acc_full, 1);
+        *abort_flag = 0;
+        fence_mbar_init();
+        prefetch_tensormap(&tm_tok);
+        prefetch_tensormap(&tm_w);
+    }
+    if (warp == 1) {
+        tmem_alloc<1>(tmem_slot, C::kTmemCols);
+        tmem_relinquish<1>();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (S > 1) {           // every CTA of the cluster is running before anyone writes into its shared memory
+        cluster_arrive();
+        cluster_wait();
+    }
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot_gen;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            for (uint32_t kb = kb0; kb < kb1; ++kb) {
+                if (!wait_bar(bar_empty + stage * 8, phase ^ 1u, ctx, kStProducerEmpty)) break;
+                mbar_arrive_expect_tx(bar_full + stage * 8, C::kStageBytes);
+                const int32_t kx = static_cast<int32_t>(kb * kBK);
+                tma_load_2d(smem_base + C::kOffW + stage * C::kWBytes, &tm_w, bar_full + stage * 8, kx,
+                            static_cast<int32_t>(ni * kBM));
+                tma_load_2d(smem_base + C::kOffT + stage * C::kTBytes, &tm_tok, bar_full + stage * 8, kx, 0);
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0 && has_k) {
+            constexpr uint32_t idesc = instr_desc_f16(BF16, kBM, TOK);
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t kb = kb0; kb < kb1; ++kb) {
+                ok = wait_bar(bar_full + stage * 8, phase, ctx, kStMmaFull);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint64_t dw = smem_desc_k_sw128(smem_base + C::kOffW + stage * C::kWBytes);
+                const uint64_t dt = smem_desc_k_sw128(smem_base + C::kOffT + stage * C::kTBytes);
+#pragma unroll
+                for (uint32_t k = 0; k < kBK / kUmmaK; ++k)
+                    umma_f16<1>(tmem_base, dw + 2 * k, dt + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                umma_commit<1>(bar_empty + stage * 8);
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+            if (ok) umma_commit<1>(bar_acc_full);
+        }
+        __syncwarp();
+    } else {
+        // ===== epilogue warps: thread = one weight row (n) of the tile, TOK partial sums (one per token) =====
+        const uint32_t q = warp & 3u;
+        const uint32_t row = q * 32u + lane;
+        bool ok = true;
+        if (has_k) {
+            ok = wait_bar(bar_acc_full, 0, ctx, kStEpiAccFull);
+            ok = __all_sync(0xffffffffu, ok);
+            tc_fence_after_sync();
+        }
+        float f[TOK];
+        if (has_k && ok) {
+#pragma unroll
+            for (uint32_t g8 = 0; g8 < TOK / 8; ++g8) {
+                uint32_t o[8];
+                tmem_ld_32x32b_x8(tmem_base + ((q * 32u) << 16) + 8u * g8, o);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[8 * g8 + i] = __uint_as_float(o[i]);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < TOK; ++i) f[i] = 0.f;
+        }
+        tc_fence_before_sync();
+        const uint32_t owner = row / rows_per;
+        const uint32_t recv_local = smem_base + C::kOffRecv;
+        if (S > 1 && owner != rank) {
+            // my partial sums for a row another CTA owns: slot `rank` of the owner's receive buffer
+            const uint32_t dst = mapa(recv_local + ((rank * rows_per + (row - owner * rows_per)) * TOK) * 4u, owner);
+#pragma unroll
+            for (uint32_t j = 0; j < TOK / 4; ++j)
+                st_cluster_v4(dst + 16u * j, f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
+        }
+        if (S > 1) {
+            __syncwarp();
+            cluster_arrive();
+            cluster_wait();
+        }
+        if (owner == rank) {
+            const float *recv = reinterpret_cast<const float *>(smem_gen + C::kOffRecv);
+            for (uint32_t r2 = 0; r2 < S; ++r2) {
+                if (r2 == rank) continue;
+                const float4 *src = reinterpret_cast<const float4 *>(recv + (r2 * rows_per + (row - rank * rows_per)) * TOK);
+#pragma unroll
+                for (uint32_t j = 0; j < TOK / 4; ++j) {
+                    const float4 v = src[j];
+                    f[4 * j] += v.x; f[4 * j + 1] += v.y; f[4 * j + 2] += v.z; f[4 * j + 3] += v.w;
+                }
+            }
+            // C[mi, n] = D[n, mi]: for each token the 32 lanes of a warp write 32 consecutive columns of C
+            const uint32_t n_glob = ni * kBM + row;
+            if (n_glob < N) {
+#pragma unroll
+                for (uint32_t mi = 0; mi < TOK; ++mi) {
+                    if (mi < M) {
+                        const uint32_t w = pack2<BF16>(f[mi], 0.f);
+                        c[static_cast<size_t>(mi) * ldc + n_glob] = static_cast<uint16_t>(w & 0xffffu);
+                    }
+                }
+            }
+        }
+    }
+    if (S > 1 && warp < 2) {      // the cluster barrier counts every thread of every CTA
+        __syncwarp();
+        cluster_arrive();
+        cluster_wait();
+    }
+    __syncthreads();
+    if (*abort_flag) __nanosleep(50000);
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc<1>(tmem_base, C::kTmemCols);
+    }
+}
+
 // Zero-fills C when k == 0 (an empty sum).
 __global__ void zero_fill_kernel(uint16_t *c, int64_t m, int64_t n, int64_t ldc) {
     const int64_t total = m * n;
@@ -827,6 +1018,50 @@ cudaError_t launch_splitk(const GemmArgs &g, const DeviceInfo &d, int split, cud
                               d.status_word);
 }
 
+template <int TOK, int STAGES, bool BF16>
+cudaError_t launch_skinny(const GemmArgs &g, const DeviceInfo &d, int split, cudaStream_t stream) {
+    using C = SnCfg<TOK, STAGES>;
+    auto kernel = hgemm_skinny_kernel<TOK, STAGES, BF16>;
+    static bool attr_done[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        if (e != cudaSuccess) return e;
+        attr_done[dev] = true;
+    }
+    CUtensorMap tm_tok, tm_w;
+    if (!make_tmap(&tm_tok, g.a, g.m, g.k, g.lda, TOK, BF16, false) ||
+        !make_tmap(&tm_w, g.b, g.n, g.k, g.ldb, kBM, BF16, false))
+        return cudaErrorInvalidValue;
+    const uint64_t tiles = (g.n + kBM - 1) / kBM;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(tiles * split), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = split;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, tm_tok, tm_w, static_cast<uint16_t *>(g.c), static_cast<uint32_t>(g.ldc),
+                              static_cast<uint32_t>(g.m), static_cast<uint32_t>(g.n), static_cast<uint32_t>(g.k),
+                              d.status_word);
+}
+
+// Cluster size for the skinny kernel: the largest S in {1,2,4,8} that keeps tiles * S within ~1.1 waves
+// of the SMs and leaves every k-slice at least four k-blocks.
+int choose_skinny_split(const GemmArgs &g, int sm_count) {
+    const int64_t tiles = (g.n + 127) / 128, k_blocks = (g.k + 63) / 64;
+    int best = 1;
+    for (int s = 2; s <= 8; s *= 2)
+        if (tiles * s * 10 <= static_cast<int64_t>(sm_count) * 11 && k_blocks >= 4 * s) best = s;
+    return best;
+}
+
 template <int CTA_GROUP, int BN, int STAGES>
 cudaError_t launch_dt(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t stream) {
     return g.bf16 ? launch<CTA_GROUP, BN, STAGES, true>(g, d, sms, stream)
@@ -877,7 +1112,10 @@ void choose_splitk(const GemmArgs &g, int sm_count, int block_n, int *bn_out, in
             if (k_blocks < 2 * s || bn / s < 8) continue;
             const int64_t ctas = tiles * s;
             if (ctas * 10 > static_cast<int64_t>(sm_count) * 11) continue;
-            if (ctas > best_ctas) { best_ctas = ctas; *bn_out = bn; *split_out = s; }
+            // on a tie a short k prefers the narrower tile with the smaller cluster (less to exchange; measured
+            // 16.5 vs 18.6 us at 128 x 4096 x 4096), a long k the deeper split (32.5 vs 37.1 us at k = 14336)
+            const bool tie_wins = ctas == best_ctas && k_blocks < 128 && s < *split_out;
+            if (ctas > best_ctas || tie_wins) { best_ctas = ctas; *bn_out = bn; *split_out = s; }
         }
     }
 }
@@ -900,6 +1138,21 @@ int hgemm_launch(const GemmArgs &g, int variant, int block_n, int max_sms, cudaS
     // variant 3 = cluster split-K; chosen automatically when one CTA per tile would leave more than
     // 40 % of the SMs without a tile and k is long enough to split
     static const int env_split = getenv("PEAKGEMM_TUNE_SPLITK") ? atoi(getenv("PEAKGEMM_TUNE_SPLITK")) : -1;
+    // variant 4 = skinny kernel (m <= 64, operands swapped); the automatic choice for such m
+    static const bool env_no_skinny = getenv("PEAKGEMM_TUNE_SKINNY") && getenv("PEAKGEMM_TUNE_SKINNY")[0] == '0';
+    if (variant == 4 || (variant == 0 && g.m <= 64 && !env_no_skinny)) {
+        if (g.m > 64) return kLaunchBadConfig;
+        int sp = choose_skinny_split(g, sms);
+        if (variant == 4 && env_split >= 1 && env_split <= 8 && (env_split & (env_split - 1)) == 0) sp = env_split;
+        if (g.m <= 16) e = g.bf16 ? launch_skinny<16, 12, true>(g, *d, sp, stream)
+                                  : launch_skinny<16, 12, false>(g, *d, sp, stream);
+        else if (g.m <= 32) e = g.bf16 ? launch_skinny<32, 10, true>(g, *d, sp, stream)
+                                       : launch_skinny<32, 10, false>(g, *d, sp, stream);
+        else e = g.bf16 ? launch_skinny<64, 8, true>(g, *d, sp, stream)
+                        : launch_skinny<64, 8, false>(g, *d, sp, stream);
+        if (e != cudaSuccess) { *cuda_err = e; return kLaunchCuda; }
+        return kLaunchOk;
+    }
     if (variant == 0 || variant == 3) {
         int sk_bn = 0, sk_s = 0;
         choose_splitk(g, sms, block_n == 256 ? 0 : block_n, &sk_bn, &sk_s);

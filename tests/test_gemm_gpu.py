@@ -92,6 +92,42 @@ def test_split_k_is_deterministic_and_refuses_unsplittable_shapes(cuda):
     assert capi.lib().pg_hgemm_ex(p, p, p, 8192, 8192, 8192, 8192, 8192, 8192, 1, 3, 0, 0, None) == 1
 
 
+# ---- skinny kernel (variant 4, m <= 64): operands swapped, optional cluster split-K over k.
+# n = 128 * tiles steers the cluster size: 16 tiles -> S=8, 32 -> 4, 64 -> 2, >= 128 -> 1.
+@pytest.mark.parametrize("dtype", [BF16, F16])
+@pytest.mark.parametrize("m,n,k", [
+    (16, 2048, 2048),      # S=8, 16 rows per CTA
+    (1, 2048, 4096),       # a single token
+    (16, 4096, 4096),      # S=4 (BASELINE config 3)
+    (17, 4096, 1024),      # 32-token tile, S=4
+    (33, 8192, 512),       # 64-token tile, S=2
+    (64, 8192, 4096),      # full 64-token tile
+    (16, 14336, 4096),     # S=1, 112 CTAs
+    (7, 1000, 264),        # tails in n and k, too few k-blocks to split
+    (16, 128, 64),         # one CTA, one k-block
+    (48, 16384 + 8, 192),  # more CTAs than SMs, ragged last tile
+])
+def test_skinny_kernel(cuda, m, n, k, dtype):
+    run_case(m, n, k, dtype, 4, 0, seed=8, gen=oracle.gemm_inputs_llm)
+
+
+def test_skinny_refuses_large_m_and_is_deterministic(cuda):
+    from peakgemm_b200 import capi
+
+    a, b = oracle.gemm_inputs_llm(16, 4096, 14336, BF16, 9)
+    ad, bd = a.cuda(), b.cuda()
+    outs = []
+    for _ in range(3):
+        c = helpers.garbage_like((16, 4096), BF16, "cuda")
+        capi.hgemm(c, ad, bd)                 # automatic choice for m <= 64
+        outs.append(c)
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    helpers.check_gemm(outs[0], a, b, exact_rows=False)
+    p = ad.data_ptr()
+    assert capi.lib().pg_hgemm_ex(p, p, p, 65, 64, 64, 64, 64, 64, 1, 4, 0, 0, None) == 1
+
+
 # ---- persistence: more tiles than CTAs, several tiles per CTA, both accumulators reused
 @pytest.mark.parametrize("variant,block_n", [(1, 64), (1, 256), (2, 64), (2, 256)])
 def test_many_tiles_per_cta(cuda, variant, block_n):
