@@ -63,7 +63,7 @@ def test_argument_checks_return_before_any_cuda_call():
     assert L.pg_hgemm(p, p, p, 64, 64, 64, 64, 64, 68, 1, None) == 3          # ldc % 8
     assert L.pg_hgemm(p, p, p, 2 ** 31, 64, 64, 64, 64, 64, 1, None) == 3     # size limit
     assert L.pg_hgemm(p + 2, p, p, 64, 64, 64, 64, 64, 64, 1, None) == 2      # misaligned
-    assert ex(p, p, p, 64, 64, 64, 64, 64, 64, 1, 3, 0, 0, None) == 1         # variant
+    assert ex(p, p, p, 64, 64, 64, 64, 64, 64, 1, 9, 0, 0, None) == 1         # variant
     assert ex(p, p, p, 64, 64, 64, 64, 64, 64, 1, 1, 100, 0, None) == 1       # block_n
     assert ex(p, p, p, 64, 64, 64, 64, 64, 64, 1, 1, 64, -1, None) == 1       # max_sms
     assert L.pg_rmsnorm_fwd(p, p, p, 0, 64, 1e-6, 1, None) == 0               # rows == 0
