@@ -329,6 +329,10 @@ def config5(args) -> None:
                              max(2, args.steps // 2))
         res["gather_row_major_bands4_ms"] = timed(lambda: sg.gathered(a, b, layout="row_major", bands=4, max_sms=140),
                                                   max(2, args.steps // 2))
+        from peakgemm_b200.dist import PeerMatrix
+
+        pm = PeerMatrix(m, n, torch.bfloat16)
+        res["gather_fused_row_major_ms"] = timed(lambda: sg.gathered_fused(pm, a, b), max(2, args.steps // 2))
     res["tflops_no_gather"] = res["flop"] / (res["no_gather_ms"] * 1e-3) / 1e12
     assert capi.device_status() == 0
     if rank == 0:

@@ -103,6 +103,42 @@ int pg_hgemm_ex(void *c, const void *a, const void *b,
                 int dtype, int variant, int block_n, int max_sms, void *stream);
 
 /*
+ * pg_hgemm with n_dst (1..8) destinations: the same C block is stored to every
+ * buffer in c_list (all with row pitch ldc), each 32 x 64 output box going out by
+ * one TMA store per destination straight from the epilogue's staging buffer.
+ *
+ * This is the fused "GEMM + all-gather" of the column-sharded layout: c_list[0] is
+ * the rank's own column block inside its full-width C, the other entries are the
+ * same block inside the PEER GPUs' C buffers (peer-mapped device pointers, e.g.
+ * from CUDA IPC), so the gather crosses NVLink tile by tile while the GEMM runs and
+ * no collective library call is needed.  Only stores ever touch peer memory.
+ * The writes are complete when the kernel has finished; ranks still need their own
+ * barrier before reading what the others wrote.  Uses the persistent kernels
+ * (variants 1 and 2).  The reference project has no multi-GPU code.
+ */
+int pg_hgemm_multi(void *const *c_list, int n_dst, const void *a, const void *b,
+                   int64_t m, int64_t n, int64_t k,
+                   int64_t lda, int64_t ldb, int64_t ldc,
+                   int dtype, int max_sms, void *stream);
+
+/*
+ * Buffers that GPUs of other processes can store into (for pg_hgemm_multi), one
+ * node.  pg_peer_alloc: cudaMalloc + CUDA IPC export (handle_out receives
+ * PG_PEER_HANDLE_BYTES bytes to send to the peers).  pg_peer_open: maps a peer's
+ * buffer into the calling process FOR THE DEVICE THAT IS CURRENT at the call (peer
+ * access is enabled lazily); the returned pointer is valid in kernels of that
+ * device.  pg_peer_close / pg_peer_free undo them.  These four calls allocate or map
+ * memory and synchronise; they belong to set-up, not to the hot path.
+ * No counterpart in the reference project (it has no multi-GPU code).
+ */
+#define PG_PEER_HANDLE_BYTES 64
+int pg_peer_alloc(size_t bytes, void **ptr, void *handle_out);
+int pg_peer_open(const void *handle, void **ptr);
+int pg_peer_close(void *ptr);
+int pg_peer_free(void *ptr);
+int pg_peer_last_cuda_error(void);
+
+/*
  * The configuration pg_hgemm would choose for this shape on a device with
  * sm_count SMs: writes variant (1 or 2) and block_n (64, 128, 256).  Pure host
  * arithmetic, needs no GPU.  (The reference's counterpart is the fixed

@@ -23,6 +23,12 @@ SIGNATURES = {
     "pg_version": (ctypes.c_char_p, []),
     "pg_hgemm": (_i, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _p]),
     "pg_hgemm_ex": (_i, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _p]),
+    "pg_hgemm_multi": (_i, [ctypes.POINTER(_p), _i, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _p]),
+    "pg_peer_alloc": (_i, [_sz, ctypes.POINTER(_p), _p]),
+    "pg_peer_open": (_i, [_p, ctypes.POINTER(_p)]),
+    "pg_peer_close": (_i, [_p]),
+    "pg_peer_free": (_i, [_p]),
+    "pg_peer_last_cuda_error": (_i, []),
     "pg_hgemm_config": (_i, [_i64, _i64, _i64, _i, ctypes.POINTER(_i), ctypes.POINTER(_i)]),
     "pg_device_status": (_i, [ctypes.POINTER(_i), _p]),
     "pg_rmsnorm_fwd": (_i, [_p, _p, _p, _i64, _i64, _f, _i, _p]),
@@ -89,6 +95,46 @@ def hgemm(c, a, b, *, variant: int = 0, block_n: int = 0, max_sms: int = 0, ldc:
                            b.stride(0) if n > 1 else k, ldc if ldc is not None else (c.stride(0) if m > 1 else n),
                            dtype_code(a.dtype), variant, block_n, max_sms, _stream_ptr(stream))
     check(st, "pg_hgemm_ex")
+
+
+def hgemm_multi(c_ptrs, a, b, ldc: int, n: int | None = None, *, max_sms: int = 0, stream=None) -> None:
+    """pg_hgemm_multi: C block = A @ B^T stored to every device address in c_ptrs (row pitch ldc elements)."""
+    m, k = a.shape
+    n = b.shape[0] if n is None else n
+    arr = (ctypes.c_void_p * len(c_ptrs))(*[ctypes.c_void_p(int(p)) for p in c_ptrs])
+    st = lib().pg_hgemm_multi(arr, len(c_ptrs), a.data_ptr(), b.data_ptr(), m, n, k, a.stride(0) if m > 1 else k,
+                              b.stride(0) if n > 1 else k, ldc, dtype_code(a.dtype), max_sms, _stream_ptr(stream))
+    check(st, "pg_hgemm_multi")
+
+
+PG_PEER_HANDLE_BYTES = 64
+
+
+def peer_alloc(nbytes: int) -> tuple[int, bytes]:
+    """(device pointer, IPC handle bytes) of a new peer-visible buffer on the current device."""
+    ptr = ctypes.c_void_p()
+    handle = ctypes.create_string_buffer(PG_PEER_HANDLE_BYTES)
+    st = lib().pg_peer_alloc(nbytes, ctypes.byref(ptr), handle)
+    if st != PG_OK:
+        raise PeakGemmError(st, f"pg_peer_alloc (cuda error {lib().pg_peer_last_cuda_error()})")
+    return int(ptr.value), bytes(handle.raw)
+
+
+def peer_open(handle: bytes) -> int:
+    """Maps a peer's buffer for kernels of the CURRENT device; returns the device pointer."""
+    ptr = ctypes.c_void_p()
+    st = lib().pg_peer_open(ctypes.c_char_p(handle), ctypes.byref(ptr))
+    if st != PG_OK:
+        raise PeakGemmError(st, f"pg_peer_open (cuda error {lib().pg_peer_last_cuda_error()})")
+    return int(ptr.value)
+
+
+def peer_close(ptr: int) -> None:
+    check(lib().pg_peer_close(ctypes.c_void_p(ptr)), "pg_peer_close")
+
+
+def peer_free(ptr: int) -> None:
+    check(lib().pg_peer_free(ctypes.c_void_p(ptr)), "pg_peer_free")
 
 
 def hgemm_config(m: int, n: int, k: int, sm_count: int = 148) -> tuple[int, int]:

@@ -74,6 +74,30 @@ int pg_hgemm_ex(void *c, const void *a, const void *b, int64_t m, int64_t n, int
     return from_launch(r, e);
 }
 
+int pg_hgemm_multi(void *const *c_list, int n_dst, const void *a, const void *b, int64_t m, int64_t n, int64_t k,
+                   int64_t lda, int64_t ldb, int64_t ldc, int dtype, int max_sms, void *stream) {
+    if (!c_list || n_dst < 1 || n_dst > 8) return PG_ERR_BAD_ARG;
+    if (m < 0 || n < 0 || k < 0 || max_sms < 0) return PG_ERR_BAD_ARG;
+    if (dtype != PG_F16 && dtype != PG_BF16) return PG_ERR_BAD_ARG;
+    if (m == 0 || n == 0) return PG_OK;
+    if (k == 0) return PG_ERR_UNSUPPORTED;                 // zero-fill of several buffers: use pg_hgemm per buffer
+    if (!a || !b) return PG_ERR_BAD_ARG;
+    if (lda < k || ldb < k || ldc < n) return PG_ERR_BAD_ARG;
+    if (n % 8 != 0 || k % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0 || ldc % 8 != 0) return PG_ERR_UNSUPPORTED;
+    if (m > kMaxDim || n > kMaxDim || k > kMaxDim) return PG_ERR_UNSUPPORTED;
+    if (!aligned16(a) || !aligned16(b)) return PG_ERR_MISALIGNED;
+    for (int i = 0; i < n_dst; ++i) {
+        if (!c_list[i]) return PG_ERR_BAD_ARG;
+        if (!aligned16(c_list[i])) return PG_ERR_MISALIGNED;
+    }
+    pg::GemmArgs g{c_list[0], a, b, m, n, k, lda, ldb, ldc, dtype == PG_BF16};
+    g.n_extra_dst = n_dst - 1;
+    for (int i = 1; i < n_dst; ++i) g.extra_dst[i - 1] = c_list[i];
+    cudaError_t e = cudaSuccess;
+    const int r = pg::hgemm_launch(g, 0, 0, max_sms, static_cast<cudaStream_t>(stream), &e);
+    return from_launch(r, e);
+}
+
 int pg_hgemm(void *c, const void *a, const void *b, int64_t m, int64_t n, int64_t k, int64_t lda,
              int64_t ldb, int64_t ldc, int dtype, void *stream) {
     return pg_hgemm_ex(c, a, b, m, n, k, lda, ldb, ldc, dtype, 0, 0, 0, stream);

@@ -75,7 +75,6 @@ constexpr uint32_t kDefaultFlags = 4u | 32u;
 
 // Tuning switches (kernel argument `flags`).
 enum : uint32_t {
-    kFlagEpiLanePoll = 1u,       // epilogue: one lane polls acc_full with a back-off
     kFlagStoreEvictFirst = 2u,   // C stores carry an L2 evict-first hint
     kFlagAEvictLast = 4u,        // A loads carry an L2 evict-last hint (keep the band's A panel resident)
     kFlagBEvictFirst = 8u,       // B loads carry an L2 evict-first hint (B streams through once per band)
@@ -117,6 +116,15 @@ struct WaitCtx {
     int *status;                    // global memory
 };
 
+// Destinations of the output tile: the epilogue stores every 32 x 64 box to each of them from the
+// same staging buffer.  One entry for a plain GEMM; one per GPU when a column-sharded caller wants C
+// replicated (the other entries then describe the same column block inside the PEERS' C buffers,
+// reached by TMA stores over NVLink — stores only: nothing is ever loaded from a peer).
+constexpr int kMaxDst = 8;
+struct DstMaps {
+    CUtensorMap m[kMaxDst];
+};
+
 // Bounded mbarrier wait.  Returns false if the wait was abandoned.  The clock is
 // only consulted every 1024 failed probes (each probe already suspends the thread
 // for a hardware-defined interval), so the common short wait costs nothing extra.
@@ -125,27 +133,6 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, const Wa
     uint64_t t0 = 0;
     uint32_t spins = 0;
     while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((++spins & 1023u) == 0) {
-            if (*ctx.abort_flag) return false;
-            const uint64_t now = globaltimer_ns();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitTimeoutNs) {
-                *ctx.abort_flag = 1;
-                atomicCAS(ctx.status, 0, code);
-                return false;
-            }
-        }
-    }
-}
-
-// Like wait_bar, for waits that normally last a whole tile: sleeps between probes.
-__device__ __forceinline__ bool wait_bar_backoff(uint32_t bar, uint32_t parity, const WaitCtx &ctx, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    uint64_t t0 = 0;
-    uint32_t spins = 0;
-    while (true) {
-        __nanosleep(200);
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 1023u) == 0) {
             if (*ctx.abort_flag) return false;
@@ -178,7 +165,7 @@ template <int CTA_GROUP, int BN, int STAGES, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                      const __grid_constant__ CUtensorMap tm_b,
-                     const __grid_constant__ CUtensorMap tm_c,
+                     const __grid_constant__ DstMaps tm_c, uint32_t n_dst,
                      uint32_t M, uint32_t N, uint32_t K, uint32_t group_m, uint32_t flags, int *status) {
     using C = Cfg<CTA_GROUP, BN, STAGES>;
     constexpr uint32_t kTileM = kBM * CTA_GROUP;
@@ -223,7 +210,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         fence_mbar_init();
         prefetch_tensormap(&tm_a);
         prefetch_tensormap(&tm_b);
-        prefetch_tensormap(&tm_c);
+        for (uint32_t d = 0; d < n_dst; ++d) prefetch_tensormap(&tm_c.m[d]);
     }
     if (warp == 1) {
         tmem_alloc<CTA_GROUP>(tmem_slot, C::kTmemCols);
@@ -340,14 +327,10 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         for (uint32_t t = worker; ok && t < total_tiles; t += workers) {
             uint32_t mi, ni;
             tile_coords(group_m, t, m_tiles, n_tiles, mi, ni, (flags & kFlagSerpentine) != 0);
-            if (flags & kFlagEpiLanePoll) {
-                // one lane polls, with a back-off: the other 31 (x4 warps) sleep at the warp barrier
-                if (lane == 0) ok = wait_bar_backoff(bar_acc_full + acc * 8, acc_phase, ctx, kStEpiAccFull);
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-            } else {
-                ok = wait_bar(bar_acc_full + acc * 8, acc_phase, ctx, kStEpiAccFull);
-                ok = __all_sync(0xffffffffu, ok);
-            }
+            // All 32 lanes probe: a failed try_wait parks the warp in hardware, so this costs nothing (a
+            // one-lane poll with __nanosleep back-off executed 40 % MORE instructions and ran 0.7 % slower).
+            ok = wait_bar(bar_acc_full + acc * 8, acc_phase, ctx, kStEpiAccFull);
+            ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             if constexpr (CTA_GROUP == 2) {
                 if (leader && e == 0 && lane == 0) mbar_arrive_cluster(peer_acc_full + acc * 8);  // relay
@@ -391,11 +374,14 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                 const uint32_t col0 = ni * BN + ch * kStoreCols;
                 if (lane == 0) {
                     if (row0 < M && col0 < N) {
-                        if (flags & kFlagStoreEvictFirst)
-                            tma_store_2d_hint(&tm_c, sbuf, static_cast<int32_t>(col0), static_cast<int32_t>(row0),
-                                              pol_store);
-                        else
-                            tma_store_2d(&tm_c, sbuf, static_cast<int32_t>(col0), static_cast<int32_t>(row0));
+                        for (uint32_t d = 0; d < n_dst; ++d) {
+                            if (flags & kFlagStoreEvictFirst)
+                                tma_store_2d_hint(&tm_c.m[d], sbuf, static_cast<int32_t>(col0),
+                                                  static_cast<int32_t>(row0), pol_store);
+                            else
+                                tma_store_2d(&tm_c.m[d], sbuf, static_cast<int32_t>(col0),
+                                             static_cast<int32_t>(row0));
+                        }
                     }
                     bulk_commit_group();
                 }
@@ -947,11 +933,16 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
         if (e != cudaSuccess) return e;
         attr_done[dev] = true;
     }
-    CUtensorMap tm_a, tm_b, tm_c;
+    CUtensorMap tm_a, tm_b;
+    DstMaps tm_c = {};
     if (!make_tmap(&tm_a, g.a, g.m, g.k, g.lda, kBM, BF16, false) ||
         !make_tmap(&tm_b, g.b, g.n, g.k, g.ldb, C::kBRows, BF16, false) ||
-        !make_tmap(&tm_c, g.c, g.m, g.n, g.ldc, kStoreRows, BF16, true))
+        !make_tmap(&tm_c.m[0], g.c, g.m, g.n, g.ldc, kStoreRows, BF16, true))
         return cudaErrorInvalidValue;
+    for (int i = 0; i < g.n_extra_dst; ++i)
+        if (!make_tmap(&tm_c.m[1 + i], g.extra_dst[i], g.m, g.n, g.ldc, kStoreRows, BF16, true))
+            return cudaErrorInvalidValue;
+    const uint32_t n_dst = 1u + static_cast<uint32_t>(g.n_extra_dst);
 
     const uint32_t tile_m = kBM * CTA_GROUP;
     const uint64_t m_tiles = (g.m + tile_m - 1) / tile_m;
@@ -978,7 +969,7 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
     static const int env_flags = getenv("PEAKGEMM_TUNE_FLAGS") ? atoi(getenv("PEAKGEMM_TUNE_FLAGS")) : -1;
     const uint32_t group_m = env_group_m > 0 ? static_cast<uint32_t>(env_group_m) : 16 / CTA_GROUP;
     const uint32_t flags = env_flags >= 0 ? static_cast<uint32_t>(env_flags) : kDefaultFlags;
-    return cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b, tm_c, static_cast<uint32_t>(g.m),
+    return cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b, tm_c, n_dst, static_cast<uint32_t>(g.m),
                               static_cast<uint32_t>(g.n), static_cast<uint32_t>(g.k), group_m, flags,
                               d.status_word);
 }
@@ -1137,6 +1128,15 @@ int hgemm_launch(const GemmArgs &g, int variant, int block_n, int max_sms, cudaS
     if (max_sms > 0 && max_sms < sms) sms = max_sms < 2 ? 2 : max_sms;
     // variant 3 = cluster split-K; chosen automatically when one CTA per tile would leave more than
     // 40 % of the SMs without a tile and k is long enough to split
+    if (g.n_extra_dst > 0 && variant == 0) {      // several destinations: the persistent TMA-store kernels only
+        variant = (g.m > 128) ? 2 : 1;
+        if (block_n == 0) {
+            int v = variant, bn = 0;
+            choose_config(g, sms, &v, &bn);
+            block_n = bn;
+        }
+    }
+    if (g.n_extra_dst > 0 && variant > 2) return kLaunchBadConfig;
     static const int env_split = getenv("PEAKGEMM_TUNE_SPLITK") ? atoi(getenv("PEAKGEMM_TUNE_SPLITK")) : -1;
     // variant 4 = skinny kernel (m <= 64, operands swapped); the automatic choice for such m
     static const bool env_no_skinny = getenv("PEAKGEMM_TUNE_SKINNY") && getenv("PEAKGEMM_TUNE_SKINNY")[0] == '0';

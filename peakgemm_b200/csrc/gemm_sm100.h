@@ -12,6 +12,8 @@ struct GemmArgs {
     int64_t m, n, k;
     int64_t lda, ldb, ldc;   // row pitches in elements
     bool bf16;               // false: fp16
+    int n_extra_dst = 0;     // further destinations of C (same extents and pitch as c), at most 7
+    void *extra_dst[7] = {};
 };
 
 enum LaunchResult { kLaunchOk = 0, kLaunchCuda = 1, kLaunchNotSm100 = 2, kLaunchBadConfig = 3 };

@@ -12,6 +12,9 @@ Layouts of a gathered C:
 
 With bands > 1 the rows of A are processed in bands: while NCCL gathers band i, the GEMM of band i+1 runs
 (leave the collective a few SMs with max_sms).  The band buffers are gathered in place.
+
+`gathered_fused` needs no collective at all: the GEMM kernel's epilogue stores each output box to every
+rank's C through peer-mapped pointers (PeerMatrix), so the gather rides NVLink tile by tile under the math.
 """
 from __future__ import annotations
 
@@ -45,6 +48,67 @@ def row_bands(m: int, bands: int, multiple: int = 256) -> list[tuple[int, int]]:
         out.append((r, min(m, r + per)))
         r += per
     return out or [(0, 0)]
+
+
+class _DeviceArray:
+    """Minimal __cuda_array_interface__ carrier so torch can wrap a raw device pointer (as int16 words)."""
+
+    def __init__(self, ptr: int, n_words: int):
+        self.__cuda_array_interface__ = {"shape": (n_words,), "typestr": "<i2", "data": (ptr, False), "version": 2}
+
+
+class PeerMatrix:
+    """A [rows, cols] 16-bit matrix allocated on every rank, whose copies on the OTHER ranks this rank's
+    kernels can store into over NVLink (one node, one process per GPU).
+
+    Each rank allocates its copy with pg_peer_alloc (cudaMalloc + CUDA IPC export) and opens every peer's
+    handle with pg_peer_open while its own device is current, which is what makes the mapping valid for
+    kernels of this device.  `local` is this rank's copy as a torch tensor; `ptrs[r]` is the device address of
+    rank r's copy as seen from this process.  Nothing in this package loads from a peer's copy.
+    """
+
+    def __init__(self, rows: int, cols: int, dtype: torch.dtype, group=None):
+        from . import capi
+
+        assert dist.is_initialized(), "PeerMatrix needs torch.distributed"
+        assert dtype in (torch.bfloat16, torch.float16)
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.rows, self.cols, self.dtype = rows, cols, dtype
+        self._capi = capi
+        self._own_ptr, handle = capi.peer_alloc(rows * cols * 2)
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, handle, group=group)
+        self.ptrs, self._opened = [], []
+        for r, h in enumerate(everyone):
+            if r == self.rank:
+                self.ptrs.append(self._own_ptr)
+            else:
+                p = capi.peer_open(h)
+                self._opened.append(p)
+                self.ptrs.append(p)
+        self.local = torch.as_tensor(_DeviceArray(self._own_ptr, rows * cols),
+                                     device=torch.device("cuda", torch.cuda.current_device())) \
+            .view(dtype).view(rows, cols)
+        dist.barrier(group=group)
+
+    def block_ptr(self, r: int, col0: int) -> int:
+        """Device address of element [0, col0] of rank r's copy."""
+        return self.ptrs[r] + 2 * col0
+
+    def close(self) -> None:
+        """Unmaps the peers' copies and frees the local one (collective: every rank must call it)."""
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        for p in self._opened:
+            self._capi.peer_close(p)
+        self._opened = []
+        dist.barrier(group=self.group)
+        if self._own_ptr:
+            self.local = None
+            self._capi.peer_free(self._own_ptr)
+            self._own_ptr = 0
 
 
 def _default_gemm(c, a, b, ldc, max_sms):
@@ -88,6 +152,22 @@ class ShardedGemm:
         if self.n_local:
             self.gemm(c_full[:, self.start:self.stop], a, b_shard, self.n, 0)
         return c_full
+
+    def gathered_fused(self, c: "PeerMatrix", a: torch.Tensor, b_shard: torch.Tensor, max_sms: int = 0) -> torch.Tensor:
+        """Replicated row-major C[m, n] with the gather fused into the GEMM: ONE kernel per rank whose epilogue
+        stores every output box to the rank's own C and, over NVLink, to the same place in every peer's C
+        (pg_hgemm_multi).  No all-gather, no re-layout; a stream-ordered barrier closes the step.  `c` is the
+        PeerMatrix that holds the result on every rank; returns this rank's copy."""
+        from . import capi
+
+        assert (c.rows, c.cols) == (a.shape[0], self.n) and c.world == self.world and c.dtype == a.dtype
+        if self.n_local:
+            order = [self.rank] + [r for r in range(self.world) if r != self.rank]
+            ptrs = [c.block_ptr(r, self.start) for r in order]
+            capi.hgemm_multi(ptrs, a, b_shard, ldc=self.n, max_sms=max_sms)
+        if self.world > 1:
+            dist.barrier(group=self.group)      # NCCL: ordered on the stream behind this rank's GEMM
+        return c.local
 
     def gathered(self, a: torch.Tensor, b_shard: torch.Tensor, layout: str = "row_major", bands: int = 1,
                  max_sms: int = 0) -> torch.Tensor:

@@ -48,7 +48,19 @@ def _worker(rank, world, port, errors):
             torch.cuda.synchronize()
             for r in range(world):
                 assert torch.equal(sm[r], got[:, r * sg.n_local:(r + 1) * sg.n_local])
+        # the gather fused into the GEMM epilogue: peer stores over NVLink, no collective
+        from peakgemm_b200.dist import PeerMatrix
+
+        pm = PeerMatrix(m, n, torch.bfloat16)
+        pm.local.fill_(float("nan"))
+        dist.barrier()
+        for max_sms in (0, 140):
+            fused = sg.gathered_fused(pm, ad, bd, max_sms=max_sms)
+            torch.cuda.synchronize()
+            assert torch.equal(fused, got), "fused gather differs from the NCCL gather"
+            dist.barrier()
         assert capi.device_status() == 0
+        pm.close()
         dist.barrier()
         dist.destroy_process_group()
     except Exception as e:  # noqa: BLE001

@@ -175,6 +175,36 @@ def test_ldc_column_block(cuda):
     assert torch.equal(full[:, :512], before[:, :512]) and torch.equal(full[:, 768:], before[:, 768:])
 
 
+def test_multi_destination_epilogue(cuda):
+    """pg_hgemm_multi on one GPU: three local buffers stand in for the peers' C; each must receive the block."""
+    from peakgemm_b200 import capi
+
+    m, n, k, n_full = 600, 512, 1024, 1536
+    a, b = oracle.gemm_inputs_uniform(m, n, k, BF16, 12)
+    fulls = [helpers.garbage_like((m, n_full), BF16, "cuda") for _ in range(3)]
+    before = fulls[1].clone()
+    ptrs = [f[:, 512:512 + n].data_ptr() for f in fulls]
+    capi.hgemm_multi(ptrs, a.cuda(), b.cuda(), ldc=n_full)
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0
+    helpers.check_gemm(fulls[0][:, 512:512 + n], a, b)
+    for f in fulls[1:]:
+        assert torch.equal(f[:, 512:512 + n], fulls[0][:, 512:512 + n])
+    assert torch.equal(fulls[1][:, :512], before[:, :512]) and torch.equal(fulls[1][:, 1024:], before[:, 1024:])
+    # a small-m case takes the one-CTA kernel
+    a2, b2 = oracle.gemm_inputs_uniform(48, 256, 512, F16, 13)
+    outs = [helpers.garbage_like((48, 256), F16, "cuda") for _ in range(2)]
+    capi.hgemm_multi([o.data_ptr() for o in outs], a2.cuda(), b2.cuda(), ldc=256)
+    torch.cuda.synchronize()
+    helpers.check_gemm(outs[0], a2, b2)
+    assert torch.equal(outs[0], outs[1])
+    L = capi.lib()
+    assert L.pg_hgemm_multi(None, 1, 0, 0, 8, 8, 8, 8, 8, 8, 1, 0, None) == 1
+    import ctypes
+    arr = (ctypes.c_void_p * 9)(*[ctypes.c_void_p(outs[0].data_ptr())] * 9)
+    assert L.pg_hgemm_multi(arr, 9, outs[0].data_ptr(), outs[0].data_ptr(), 8, 8, 8, 8, 8, 8, 1, 0, None) == 1
+
+
 def test_argument_errors(cuda):
     from peakgemm_b200 import capi
 
