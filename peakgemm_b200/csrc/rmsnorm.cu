@@ -270,6 +270,9 @@ rmsnorm_bwd_kernel(uint4 *__restrict__ dx, float *__restrict__ partial, const ui
 __global__ void __launch_bounds__(1024)
 rmsnorm_dgamma_reduce_kernel(float *__restrict__ dgamma, const float *__restrict__ partial, int nparts, int h4) {
     __shared__ float4 red[32][33];
+    // Launched with programmatic stream serialization: this grid may be scheduled while the backward kernel
+    // is still draining; nothing of its output is touched before the dependency has fully completed.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int cx = threadIdx.x & 31, sl = threadIdx.x >> 5;
     const int col = blockIdx.x * 32 + cx;
     float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -441,9 +444,20 @@ cudaError_t rmsnorm_bwd_launch(const RmsBwdArgs &a, int ctas, cudaStream_t strea
     }
     if (e != cudaSuccess) return e;
     const int h4 = static_cast<int>(a.h / 4);
-    rmsnorm_dgamma_reduce_kernel<<<(h4 + 31) / 32, 1024, 0, stream>>>(
-        a.dgamma, static_cast<const float *>(a.workspace), ctas, h4);
-    return cudaGetLastError();
+    // Programmatic dependent launch: the reduction's launch latency (~3 us of a ~140 us step) overlaps the
+    // tail of the backward kernel; griddepcontrol.wait inside it orders the data.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>((h4 + 31) / 32), 1, 1);
+    cfg.blockDim = dim3(1024, 1, 1);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, rmsnorm_dgamma_reduce_kernel, a.dgamma,
+                              static_cast<const float *>(a.workspace), ctas, h4);
 }
 
 }  // namespace pg

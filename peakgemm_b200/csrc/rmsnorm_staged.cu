@@ -155,6 +155,10 @@ rms_staged_kernel(uint4 *__restrict__ out, float *__restrict__ partial, const ui
     const WaitCtx ctx{abort_flag, status};
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if constexpr (BWD) {
+        // The dgamma reduction that follows may be launched early (it waits on griddepcontrol.wait).
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
     const int consumers = T * G;
     const int group_warps = T >> 5;
     // rows of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...; its i-th row goes to slot i % stages, group i % G
