@@ -265,8 +265,11 @@ rms_staged_kernel(uint4 *__restrict__ out, float *__restrict__ partial, const ui
                 S1 += s_red[it][warp - gw + w][0];
                 if constexpr (BWD) S2 += s_red[it][warp - gw + w][1];
             }
-            const float rstd = 1.0f / sqrtf(S1 / h_f + eps);
-            const float cm = (S2 * rstd) / h_f;     // backward: mean_j(g * xhat)
+            // rsqrt.approx (2 ulp of fp32) and a multiply by 1/h instead of sqrt + two IEEE divisions: ~45 fewer
+            // instructions per thread and row; the result is rounded to a 16-bit type anyway
+            const float inv_h = 1.0f / h_f;
+            const float rstd = rsqrtf(fmaf(S1, inv_h, eps));
+            const float cm = (S2 * rstd) * inv_h;   // backward: mean_j(g * xhat)
 #pragma unroll
             for (int j = 0; j < VPT; ++j) {
                 const int idx = t + T * j;
