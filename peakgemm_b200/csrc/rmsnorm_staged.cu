@@ -356,12 +356,21 @@ Plan make_plan(int64_t h, bool bwd) {
     if (p.G > 8) p.G = 8;
     for (int s = kMaxStages; s >= 2; --s) {
         const Layout l = make_layout(static_cast<int>(h), bwd, s);
-        if (l.total <= kSmemBudget) {
-            p.stages = s;
-            p.smem = l.total;
-            p.ok = true;
-            return p;
-        }
+        if (l.total > kSmemBudget) continue;
+        // The ring depth must be a multiple of the number of groups, so that a slot is always consumed by the SAME
+        // group.  A consumer waits on full[slot] by phase parity only, which is sound as long as it can be at most
+        // one phase early: true for a group that consumed the slot's previous round itself.  With a rotating
+        // assignment a group that runs ahead can poll a slot two phases early, see the parity of the phase before
+        // last as "complete", read a slot that is still being filled and arrive on empty[slot] out of turn; the
+        // surplus arrival breaks the barrier (seen as "unspecified launch failure" once the ring wrapped, i.e. only
+        // with hundreds of rows per CTA).
+        if (p.G > s) p.G = s;
+        const int depth = s / p.G * p.G;
+        const Layout ld = make_layout(static_cast<int>(h), bwd, depth);
+        p.stages = depth;
+        p.smem = ld.total;
+        p.ok = true;
+        return p;
     }
     return p;
 }
