@@ -35,8 +35,14 @@ using namespace ptx;
 
 namespace {
 
-constexpr int kMaxConsumers = 512;                // consumer threads per CTA (kG groups x T threads)
-constexpr int kThreads = kMaxConsumers + 32;      // + producer warp
+// Consumer threads per CTA (G groups x T threads); the producer warp comes on top.  Forward: up to 960 (more rows
+// in flight per SM: its per-row chain is latency-bound and needs few registers); backward: 512 (its dgamma
+// shares and both operands need ~96 registers per thread).
+template <bool BWD>
+struct Threads {
+    static constexpr int kConsumers = BWD ? 512 : 960;     // + 32 <= 1024 threads per CTA
+    static constexpr int kTotal = kConsumers + 32;
+};
 constexpr int kMaxStages = 16;
 constexpr uint64_t kWaitTimeoutNs = 2000000000ull;
 constexpr uint32_t kSmemBudget = 200 * 1024;      // bytes of dynamic shared memory we ask for at most
@@ -132,23 +138,25 @@ __host__ __device__ inline Layout make_layout(int h, bool bwd, int stages) {
     l.row_bytes = static_cast<uint32_t>(h) * 2;
     l.slot_bytes = l.row_bytes * (bwd ? 2 : 1);
     l.off_red = l.off_slot + stages * l.slot_bytes;
-    l.off_bar = l.off_red + 2 * 16 * 2 * static_cast<uint32_t>(sizeof(float));   // [2 buffers][16 warps][2]
+    l.off_bar = l.off_red + 2 * 32 * 2 * static_cast<uint32_t>(sizeof(float));   // [2 buffers][32 warps][2]
     l.total = l.off_bar + 2 * stages * 8 + 16;
     return l;
 }
 
 // T threads per group (a multiple of 32), G groups, VPT * T >= h / 8.
 template <bool BWD, int VPT, bool BF16>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(Threads<BWD>::kTotal, 1)
 rms_staged_kernel(uint4 *__restrict__ out, float *__restrict__ partial, const uint4 *__restrict__ x,
                   const uint4 *__restrict__ dy, const float *__restrict__ gamma, int64_t rows, int h8,
                   float h_f, float eps, int stages, int T, int G, int *status) {
     extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int kMaxConsumers = Threads<BWD>::kConsumers;
+    constexpr int kThreads = Threads<BWD>::kTotal;
     const int h = h8 * 8;
     const Layout L = make_layout(h, BWD, stages);
     const uint32_t sbase = smem_u32(smem);
     const float *s_gamma = reinterpret_cast<const float *>(smem);
-    float(*s_red)[16][2] = reinterpret_cast<float(*)[16][2]>(smem + L.off_red);
+    float(*s_red)[32][2] = reinterpret_cast<float(*)[32][2]>(smem + L.off_red);
     const uint32_t bar_full = sbase + L.off_bar;
     const uint32_t bar_empty = bar_full + stages * 8;
     volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem + L.off_bar + 2 * stages * 8);
@@ -340,19 +348,20 @@ Plan make_plan(int64_t h, bool bwd) {
     Plan p{false, 0, 0, 0, 0, 0};
     const int64_t h8 = h / 8;
     if (h8 < 32 || h8 > 2048) return p;
-    // aim at 4 vectors per thread; groups of 32..256 threads
-    int T = static_cast<int>((h8 / 4 + 31) / 32 * 32);
+    // groups of 32..256 threads; aim at 4 vectors per thread in the backward pass and 2 in the forward pass
+    // (measured at h = 4096 with up to 960 consumer threads: forward 91.0 us with T = 256 / 3 groups against
+    // 100.0 us with T = 128 / 7 groups; backward 136 us with T = 128 against 158 us with T = 256)
+    const int per_thread = bwd ? 4 : 2;
+    int T = static_cast<int>((h8 / per_thread + 31) / 32 * 32);
     if (T < 32) T = 32;
     if (T > 256) T = 256;
     // Benchmark override, read once: PEAKGEMM_TUNE_RMS_T = threads per consumer group (32..256).
-    // Measured on [32768, H] bf16: T=128 is best at H=4096 (T=64: -8 % fwd, -40 % bwd; T=256: -15 %),
-    // T=256 at H=8192 (T=128: -18 % fwd, -40 % bwd).
     static const int env_t = getenv("PEAKGEMM_TUNE_RMS_T") ? atoi(getenv("PEAKGEMM_TUNE_RMS_T")) : 0;
     if (env_t >= 32 && env_t <= 256 && env_t % 32 == 0 && (h8 + env_t - 1) / env_t <= 8) T = env_t;
     const int need = static_cast<int>((h8 + T - 1) / T);
     p.vpt = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
     p.T = T;
-    p.G = kMaxConsumers / T;
+    p.G = (bwd ? Threads<true>::kConsumers : Threads<false>::kConsumers) / T;
     if (p.G > 8) p.G = 8;
     for (int s = kMaxStages; s >= 2; --s) {
         const Layout l = make_layout(static_cast<int>(h), bwd, s);
@@ -407,7 +416,7 @@ cudaError_t launch_one(void *out, float *partial, const void *x, const void *dy,
         if (e != cudaSuccess) return e;
         attr_done[dev] = true;
     }
-    kernel<<<grid, kThreads, p.smem, stream>>>(static_cast<uint4 *>(out), partial, static_cast<const uint4 *>(x),
+    kernel<<<grid, Threads<BWD>::kTotal, p.smem, stream>>>(static_cast<uint4 *>(out), partial, static_cast<const uint4 *>(x),
                                                static_cast<const uint4 *>(dy), gamma, rows,
                                                static_cast<int>(h / 8), static_cast<float>(h), eps, p.stages, p.T,
                                                p.G, status);
