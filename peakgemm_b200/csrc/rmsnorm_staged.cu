@@ -144,7 +144,11 @@ __host__ __device__ inline Layout make_layout(int h, bool bwd, int stages) {
 }
 
 // T threads per group (a multiple of 32), G groups, VPT * T >= h / 8.
-template <bool BWD, int VPT, bool BF16>
+// INCR: the consumers keep slot / phase / output-row pointer incrementally instead of deriving them from the row
+// index with two runtime divisions.  Same results; which form is faster depends on the shape (measured on
+// [32768, h] bf16: backward h = 8192 269 -> 250 us with INCR, but forward h = 4096 91 -> 98 us and backward
+// h = 4096 136 -> 139 us), so the host picks per shape.
+template <bool BWD, int VPT, bool BF16, bool INCR>
 __global__ void __launch_bounds__(Threads<BWD>::kTotal, 1)
 rms_staged_kernel(uint4 *__restrict__ out, float *__restrict__ partial, const uint4 *__restrict__ x,
                   const uint4 *__restrict__ dy, const float *__restrict__ gamma, int64_t rows, int h8,
@@ -213,10 +217,24 @@ rms_staged_kernel(uint4 *__restrict__ out, float *__restrict__ partial, const ui
         // ===== consumers =====
         const int gw = t >> 5;                   // warp within the group
         int it = 0;
+        // the group's rows are i = g, g + G, ...; slot = i % stages and phase = (i / stages) & 1 are kept
+        // incrementally (stages is a multiple of G), as is the output row pointer
+        int slot = g;
+        uint32_t phase = 0;
+        uint4 *orow = out + (static_cast<int64_t>(blockIdx.x) + static_cast<int64_t>(g) * gridDim.x) * h8;
+        const int64_t orow_step = static_cast<int64_t>(G) * gridDim.x * h8;
         for (int64_t i = g; i < my_rows; i += G, it ^= 1) {
-            const int slot = static_cast<int>(i % stages);
-            const uint32_t phase = static_cast<uint32_t>(i / stages) & 1u;
-            const int64_t row = blockIdx.x + i * gridDim.x;
+            if constexpr (INCR) {
+                if (i != g) {
+                    slot += G;
+                    if (slot >= stages) { slot -= stages; phase ^= 1u; }
+                    orow += orow_step;
+                }
+            } else {
+                slot = static_cast<int>(i % stages);
+                phase = static_cast<uint32_t>(i / stages) & 1u;
+                orow = out + (static_cast<int64_t>(blockIdx.x) + i * gridDim.x) * h8;
+            }
             bool ok = wait_bar(bar_full + slot * 8, phase, ctx, kStRmsConsumer);
             ok = __all_sync(0xffffffffu, ok);
             // A warp that gave up still walks to the barrier below (on zeros), where the whole group
@@ -300,7 +318,7 @@ rms_staged_kernel(uint4 *__restrict__ out, float *__restrict__ partial, const ui
 #pragma unroll
                         for (int e = 0; e < 8; ++e) o[e] = (xf[e] * rstd) * gm[e];
                     }
-                    __stcs(out + row * h8 + idx, pack8<BF16>(o));
+                    __stcs(orow + idx, pack8<BF16>(o));
                 }
             }
         }
@@ -403,11 +421,11 @@ cudaError_t device_setup(int *sms, int **status) {
     return cudaSuccess;
 }
 
-template <bool BWD, int VPT, bool BF16>
+template <bool BWD, int VPT, bool BF16, bool INCR>
 cudaError_t launch_one(void *out, float *partial, const void *x, const void *dy, const float *gamma,
                        int64_t rows, int64_t h, float eps, const Plan &p, int grid, int *status,
                        cudaStream_t stream) {
-    auto kernel = rms_staged_kernel<BWD, VPT, BF16>;
+    auto kernel = rms_staged_kernel<BWD, VPT, BF16, INCR>;
     static bool attr_done[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -426,10 +444,15 @@ cudaError_t launch_one(void *out, float *partial, const void *x, const void *dy,
 template <bool BWD>
 cudaError_t launch_any(void *out, float *partial, const void *x, const void *dy, const float *gamma, int64_t rows,
                        int64_t h, float eps, bool bf16, const Plan &p, int grid, int *status, cudaStream_t stream) {
-#define PG_RMS_CASE(V)                                                                                       \
-    if (p.vpt == V)                                                                                          \
-        return bf16 ? launch_one<BWD, V, true>(out, partial, x, dy, gamma, rows, h, eps, p, grid, status, stream) \
-                    : launch_one<BWD, V, false>(out, partial, x, dy, gamma, rows, h, eps, p, grid, status, stream);
+    const bool incr = BWD && h > 4096;
+#define PG_RMS_CASE(V)                                                                                             \
+    if (p.vpt == V) {                                                                                              \
+        if (incr)                                                                                                  \
+            return bf16 ? launch_one<BWD, V, true, true>(out, partial, x, dy, gamma, rows, h, eps, p, grid, status, stream)   \
+                        : launch_one<BWD, V, false, true>(out, partial, x, dy, gamma, rows, h, eps, p, grid, status, stream); \
+        return bf16 ? launch_one<BWD, V, true, false>(out, partial, x, dy, gamma, rows, h, eps, p, grid, status, stream)      \
+                    : launch_one<BWD, V, false, false>(out, partial, x, dy, gamma, rows, h, eps, p, grid, status, stream);    \
+    }
     PG_RMS_CASE(1)
     PG_RMS_CASE(2)
     PG_RMS_CASE(4)
