@@ -103,6 +103,17 @@ int pg_hgemm_ex(void *c, const void *a, const void *b,
                 int dtype, int variant, int block_n, int max_sms, void *stream);
 
 /*
+ * fp32 C[m,n] = A[m,k] * B[n,k]^T with true fp32 FMA accumulation (CUDA cores, no
+ * TF32): the float branch of the gemm_peak operator, where the reference calls
+ * sgemm::sgemm_peak (src/ops/gemm.cpp:34-43, src/impl/sgemm_impl.h:310-320) — by its
+ * README an unoptimised reference path (README.md:46-47), and not the hot path here
+ * either.  Pitches in elements; k, lda, ldb, ldc multiples of 4; 16-byte aligned
+ * pointers; any m, n.
+ */
+int pg_sgemm(float *c, const float *a, const float *b, int64_t m, int64_t n, int64_t k,
+             int64_t lda, int64_t ldb, int64_t ldc, void *stream);
+
+/*
  * pg_hgemm with n_dst (1..8) destinations: the same C block is stored to every
  * buffer in c_list (all with row pitch ldc), each 32 x 64 output box going out by
  * one TMA store per destination straight from the epilogue's staging buffer.

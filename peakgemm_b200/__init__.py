@@ -39,8 +39,8 @@ def gemm_peak(c: torch.Tensor, a: torch.Tensor, b: torch.Tensor) -> None:
 
     Same contract as the reference wrapper (PeakGemm/__init__.py:21-34): leading
     dimensions of ``a`` and ``c`` are flattened, ``b`` is stored ``[n, k]``,
-    nothing is returned.  float32 passes the reference's dtype assert but is then
-    refused by the operator (only float16 / bfloat16 kernels are built here).
+    nothing is returned.  float16 / bfloat16 run on the tcgen05 kernels; float32 runs on
+    a plain fp32 FFMA kernel, as in the reference (its unoptimised sgemm path).
     """
     assert a.dtype in [torch.float, torch.half, torch.bfloat16]
     k = a.shape[-1]

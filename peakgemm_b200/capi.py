@@ -29,6 +29,7 @@ SIGNATURES = {
     "pg_peer_close": (_i, [_p]),
     "pg_peer_free": (_i, [_p]),
     "pg_peer_last_cuda_error": (_i, []),
+    "pg_sgemm": (_i, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _p]),
     "pg_hgemm_config": (_i, [_i64, _i64, _i64, _i, ctypes.POINTER(_i), ctypes.POINTER(_i)]),
     "pg_device_status": (_i, [ctypes.POINTER(_i), _p]),
     "pg_rmsnorm_fwd": (_i, [_p, _p, _p, _i64, _i64, _f, _i, _p]),
@@ -135,6 +136,14 @@ def peer_close(ptr: int) -> None:
 
 def peer_free(ptr: int) -> None:
     check(lib().pg_peer_free(ctypes.c_void_p(ptr)), "pg_peer_free")
+
+
+def sgemm(c, a, b, stream=None) -> None:
+    """pg_sgemm on float32 torch CUDA tensors (2-D, row-major): C = A @ B^T."""
+    m, k = a.shape
+    n = b.shape[0]
+    check(lib().pg_sgemm(c.data_ptr(), a.data_ptr(), b.data_ptr(), m, n, k, a.stride(0) if m > 1 else k,
+                         b.stride(0) if n > 1 else k, c.stride(0) if m > 1 else n, _stream_ptr(stream)), "pg_sgemm")
 
 
 def hgemm_config(m: int, n: int, k: int, sm_count: int = 148) -> tuple[int, int]:

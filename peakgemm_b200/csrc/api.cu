@@ -7,6 +7,7 @@
 #include "../../include/peakgemm.h"
 #include "gemm_sm100.h"
 #include "rmsnorm.h"
+#include "sgemm.h"
 
 namespace {
 
@@ -101,6 +102,19 @@ int pg_hgemm_multi(void *const *c_list, int n_dst, const void *a, const void *b,
 int pg_hgemm(void *c, const void *a, const void *b, int64_t m, int64_t n, int64_t k, int64_t lda,
              int64_t ldb, int64_t ldc, int dtype, void *stream) {
     return pg_hgemm_ex(c, a, b, m, n, k, lda, ldb, ldc, dtype, 0, 0, 0, stream);
+}
+
+int pg_sgemm(float *c, const float *a, const float *b, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb,
+             int64_t ldc, void *stream) {
+    if (m < 0 || n < 0 || k < 0) return PG_ERR_BAD_ARG;
+    if (m == 0 || n == 0) return PG_OK;
+    if (!c || (k > 0 && (!a || !b))) return PG_ERR_BAD_ARG;
+    if (lda < k || ldb < k || ldc < n) return PG_ERR_BAD_ARG;
+    if (k % 4 != 0 || lda % 4 != 0 || ldb % 4 != 0 || ldc % 4 != 0) return PG_ERR_UNSUPPORTED;
+    if (m > kMaxDim || n > kMaxDim || k > kMaxDim) return PG_ERR_UNSUPPORTED;
+    if (!aligned16(c) || (k > 0 && (!aligned16(a) || !aligned16(b)))) return PG_ERR_MISALIGNED;
+    const cudaError_t e = pg::sgemm_launch(c, a, b, m, n, k, lda, ldb, ldc, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? PG_OK : cuda_fail(e);
 }
 
 int pg_hgemm_config(int64_t m, int64_t n, int64_t k, int sm_count, int *variant, int *block_n) {

@@ -8,8 +8,9 @@
 //   asynchronous launch, nothing returned, `c` written in place.
 // Differences, all on the error side: arguments the reference leaves unchecked
 // (device, dtype equality, shapes against m/n/k) raise c10::Error here instead of
-// reading out of bounds, and fp32/fp64 inputs are refused (the reference sends
-// fp32 to its unoptimised sgemm path, src/ops/gemm.cpp:34-43).
+// reading out of bounds, and fp64 inputs are refused with a message (in the reference
+// they fall into the float branch and throw inside data_ptr<float>, gemm.cpp:34-37).
+// float32 goes to pg_sgemm, as the reference sends it to sgemm_peak.
 //
 // rms_norm_fwd / rms_norm_bwd have no counterpart in the reference; they follow
 // the same conventions: outputs first, caller-allocated, in place, return ().
@@ -46,9 +47,15 @@ void gemm_peak(Tensor &c, Tensor &a, Tensor &b, int64_t m, int64_t n, int64_t k)
                 "gemm_peak: a, b, c must have one dtype");
     TORCH_CHECK(m >= 0 && n >= 0 && k >= 0 && a.numel() == m * k && b.numel() == n * k && c.numel() == m * n,
                 "gemm_peak: tensor sizes do not match m, n, k");
-    const int dt = dtype_code(a, "gemm_peak");
     c10::DeviceGuard device_guard(a.device());
     auto stream = at::cuda::getCurrentCUDAStream();
+    if (a.scalar_type() == at::kFloat) {      // the reference's sgemm_peak branch (src/ops/gemm.cpp:34-43)
+        check_status(pg_sgemm(c.data_ptr<float>(), a.data_ptr<float>(), b.data_ptr<float>(), m, n, k, k, k, n,
+                              stream.stream()),
+                     "gemm_peak");
+        return;
+    }
+    const int dt = dtype_code(a, "gemm_peak");
     check_status(pg_hgemm(c.data_ptr(), a.data_ptr(), b.data_ptr(), m, n, k, k, k, n, dt, stream.stream()),
                  "gemm_peak");
 }

@@ -20,7 +20,7 @@ def declared_functions():
 
 def test_header_declares_the_expected_surface():
     names = declared_functions()
-    for must in ("pg_hgemm", "pg_hgemm_ex", "pg_hgemm_multi", "pg_hgemm_config", "pg_rmsnorm_fwd", "pg_rmsnorm_bwd",
+    for must in ("pg_hgemm", "pg_hgemm_ex", "pg_hgemm_multi", "pg_sgemm", "pg_hgemm_config", "pg_rmsnorm_fwd", "pg_rmsnorm_bwd",
                  "pg_rmsnorm_bwd_workspace_bytes", "pg_rmsnorm_bwd_static", "pg_device_status",
                  "pg_status_string", "pg_last_cuda_error", "pg_version", "pg_peer_alloc", "pg_peer_open",
                  "pg_peer_close", "pg_peer_free"):
@@ -67,6 +67,9 @@ def test_argument_checks_return_before_any_cuda_call():
     assert ex(p, p, p, 64, 64, 64, 64, 64, 64, 1, 9, 0, 0, None) == 1         # variant
     assert ex(p, p, p, 64, 64, 64, 64, 64, 64, 1, 1, 100, 0, None) == 1       # block_n
     assert ex(p, p, p, 64, 64, 64, 64, 64, 64, 1, 1, 64, -1, None) == 1       # max_sms
+    assert L.pg_sgemm(p, p, p, 0, 8, 8, 8, 8, 8, None) == 0
+    assert L.pg_sgemm(p, p, p, 8, 8, 6, 8, 8, 8, None) == 3                   # k % 4
+    assert L.pg_sgemm(None, p, p, 8, 8, 8, 8, 8, 8, None) == 1
     assert L.pg_rmsnorm_fwd(p, p, p, 0, 64, 1e-6, 1, None) == 0               # rows == 0
     assert L.pg_rmsnorm_fwd(p, p, p, 4, 60, 1e-6, 1, None) == 3               # h % 8
     assert L.pg_rmsnorm_fwd(p, p, p, 4, 0, 1e-6, 1, None) == 1

@@ -42,14 +42,33 @@ def test_op_runs_on_current_stream_and_raw_op(cuda):
     helpers.check_gemm(c, a, b)
 
 
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (300, 200, 1000), (1, 8, 4), (1024, 1024, 2048), (130, 132, 36)])
+def test_gemm_peak_float32_branch(cuda, m, n, k):
+    """The operator's float branch (the reference's sgemm_peak): fp32 FMA accumulation, absolute bound 1e-4 * k/4096
+    floor 1e-4 as in test/cpp/test_gemm_float.cpp:151, against a float64 product of the same inputs."""
+    import PeakGemm
+
+    g = torch.Generator().manual_seed(50)
+    a = torch.rand(m, k, generator=g) * 2 - 1
+    b = torch.rand(n, k, generator=g) * 2 - 1
+    c = torch.randn(m, n, device="cuda")
+    PeakGemm.gemm_peak(c, a.cuda(), b.cuda())
+    torch.cuda.synchronize()
+    ref = (a.double() @ b.double().t())
+    err = (c.cpu().double() - ref).abs().max().item()
+    assert err <= 1e-4 * max(1.0, k / 1024), err
+
+
 def test_op_errors(cuda):
     import PeakGemm
 
     a = torch.zeros(64, 64, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(RuntimeError):
         PeakGemm.gemm_peak(torch.zeros(64, 64, dtype=torch.float16, device="cuda"), a, a)   # dtype mismatch
+    with pytest.raises(AssertionError):
+        PeakGemm.gemm_peak(a.double(), a.double(), a.double())        # the wrapper's dtype assert (__init__.py:26)
     with pytest.raises(RuntimeError):
-        PeakGemm.gemm_peak(a.float(), a.float(), a.float())                                  # fp32 not built
+        torch.ops.PeakGemm.gemm_peak(a.double(), a.double(), a.double(), 64, 64, 64)         # fp64 not built
     with pytest.raises(RuntimeError):
         PeakGemm.gemm_peak(a, a.t(), a)                                                      # not contiguous
     with pytest.raises(RuntimeError):
