@@ -226,6 +226,28 @@ def rmsnorm_numbers(peaks: dict, steps: int, warmup: int, rows: int = 32768) -> 
     return out
 
 
+def probes() -> dict:
+    """What this GPU allows with nothing in the way (pg_probe_*): back-to-back tcgen05.mma on resident tiles, and a
+    streaming copy.  The reference's counterparts are test/cpp/test_wmma_compute.cpp and test_memory_bandwidth.cpp."""
+    import torch
+
+    from peakgemm_b200 import capi
+
+    out = {}
+    for name, is_bf16 in (("bf16", True), ("fp16", False)):
+        burst, ms_b = capi.probe_tensor_peak(is_bf16, 2000)          # ~0.7 ms: the length of one 8192^3 GEMM
+        sustained, ms_s = capi.probe_tensor_peak(is_bf16, 60000)     # ~25 ms under the power cap
+        out[f"mma_{name}_tflops_burst"] = burst
+        out[f"mma_{name}_tflops_sustained"] = sustained
+    src = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")
+    dst = torch.empty_like(src)
+    t = time_cuda(lambda: capi.probe_copy(dst, src), 20, 3)
+    out["copy_gbs"] = 2 * src.numel() / t / 1e6
+    out["what"] = "tcgen05.mma.cta_group::2 256x256x16 issued back to back on all SM pairs, pseudo-random operands " \
+                  "resident in shared memory, no loads; 128-bit streaming copy of 512 MiB"
+    return out
+
+
 def shape_sweep(peaks: dict) -> list:
     """BASELINE configs 2 and 3: every shape, ours (automatic configuration) against cuBLAS on the same GPU.
 
@@ -355,6 +377,7 @@ def main() -> None:
     ap.add_argument("--config5", action="store_true",
                     help="BASELINE config 5 (32768 x 32768 x 16384 sharded over the ranks, with and without the "
                          "all-gather); prints one JSON object and exits")
+    ap.add_argument("--probe", action="store_true", help="run only the roofline probes; prints one JSON object and exits")
     ap.add_argument("--sweep", action="store_true",
                     help="BASELINE configs 2 and 3 (every shape) against cuBLAS; prints one JSON object and exits")
     ap.add_argument("--only-rmsnorm", type=int, default=0, metavar="ROWS",
@@ -387,6 +410,9 @@ def main() -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     peaks = measured_peaks()
+    if args.probe:
+        print(json.dumps({"probe": probes()}))
+        return
     if args.sweep:
         print(json.dumps({"sweep": shape_sweep(peaks), "peaks": {k: v for k, v in peaks.items() if not isinstance(v, dict)}}))
         return
@@ -526,6 +552,7 @@ def main() -> None:
             line["reference_kernel_on_this_gpu"] = {"tflops": flops_step / (t_ref * 1e-3) / 1e12, "ms": t_ref,
                                                     "what": "reference mma.sync hgemm_peak compiled for sm_100a"}
         line["rmsnorm"] = rmsnorm_numbers(peaks, args.steps, args.warmup)
+        line["probe"] = probes()
         line["cpu_baseline"] = cpu_gemm_baseline()
     elif rank == 0 and world > 1:
         line["e2e"] = None

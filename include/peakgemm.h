@@ -230,6 +230,19 @@ int pg_rmsnorm_bwd_static(void *dx, float *dgamma, const void *dy, const void *x
                           const float *gamma, int64_t rows, int64_t h, float eps,
                           int dtype, void *stream);
 
+/*
+ * Roofline probes, the sm_100a counterparts of the reference's stand-alone probes
+ * (test/cpp/test_wmma_compute.cpp:142-173, the README's "PEAK" column; and
+ * test/cpp/test_memory_bandwidth.cpp:95-114).
+ * pg_probe_tensor_peak: every SM pair issues tcgen05.mma.cta_group::2 256x256x16
+ * back to back on pseudo-random operand tiles resident in shared memory, `iters`
+ * rounds of k = 64, no loads in the loop; writes the TFLOP/s reached (and the
+ * milliseconds).  Synchronises the device's default stream; allocates nothing.
+ * pg_probe_copy: 128-bit streaming copy, asynchronous on `stream`.
+ */
+int pg_probe_tensor_peak(int dtype, int iters, float *tflops_out, float *ms_out);
+int pg_probe_copy(void *dst, const void *src, size_t bytes, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -30,6 +30,8 @@ SIGNATURES = {
     "pg_peer_free": (_i, [_p]),
     "pg_peer_last_cuda_error": (_i, []),
     "pg_sgemm": (_i, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _p]),
+    "pg_probe_tensor_peak": (_i, [_i, _i, ctypes.POINTER(_f), ctypes.POINTER(_f)]),
+    "pg_probe_copy": (_i, [_p, _p, _sz, _p]),
     "pg_hgemm_config": (_i, [_i64, _i64, _i64, _i, ctypes.POINTER(_i), ctypes.POINTER(_i)]),
     "pg_device_status": (_i, [ctypes.POINTER(_i), _p]),
     "pg_rmsnorm_fwd": (_i, [_p, _p, _p, _i64, _i64, _f, _i, _p]),
@@ -144,6 +146,19 @@ def sgemm(c, a, b, stream=None) -> None:
     n = b.shape[0]
     check(lib().pg_sgemm(c.data_ptr(), a.data_ptr(), b.data_ptr(), m, n, k, a.stride(0) if m > 1 else k,
                          b.stride(0) if n > 1 else k, c.stride(0) if m > 1 else n, _stream_ptr(stream)), "pg_sgemm")
+
+
+def probe_tensor_peak(dtype_is_bf16: bool = True, iters: int = 20000) -> tuple[float, float]:
+    """(TFLOP/s, ms) of the back-to-back tcgen05.mma probe on all SM pairs."""
+    tf, ms = ctypes.c_float(0), ctypes.c_float(0)
+    check(lib().pg_probe_tensor_peak(PG_BF16 if dtype_is_bf16 else PG_F16, iters, ctypes.byref(tf), ctypes.byref(ms)),
+          "pg_probe_tensor_peak")
+    return tf.value, ms.value
+
+
+def probe_copy(dst, src, stream=None) -> None:
+    check(lib().pg_probe_copy(dst.data_ptr(), src.data_ptr(), src.numel() * src.element_size(), _stream_ptr(stream)),
+          "pg_probe_copy")
 
 
 def hgemm_config(m: int, n: int, k: int, sm_count: int = 148) -> tuple[int, int]:

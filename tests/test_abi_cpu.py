@@ -23,7 +23,7 @@ def test_header_declares_the_expected_surface():
     for must in ("pg_hgemm", "pg_hgemm_ex", "pg_hgemm_multi", "pg_sgemm", "pg_hgemm_config", "pg_rmsnorm_fwd", "pg_rmsnorm_bwd",
                  "pg_rmsnorm_bwd_workspace_bytes", "pg_rmsnorm_bwd_static", "pg_device_status",
                  "pg_status_string", "pg_last_cuda_error", "pg_version", "pg_peer_alloc", "pg_peer_open",
-                 "pg_peer_close", "pg_peer_free"):
+                 "pg_peer_close", "pg_peer_free", "pg_probe_tensor_peak", "pg_probe_copy"):
         assert must in names
 
 

@@ -302,3 +302,17 @@ def test_deterministic(cuda):
         outs.append(c)
     torch.cuda.synchronize()
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+
+
+def test_roofline_probes(cuda):
+    """The probes run and report plausible figures (tensor: between the reference kernel's and nominal peak)."""
+    from peakgemm_b200 import capi
+
+    tf, ms = capi.probe_tensor_peak(True, 2000)
+    assert 500.0 < tf < 2600.0 and ms > 0
+    src = torch.arange(1 << 22, dtype=torch.int32, device="cuda")
+    dst = torch.zeros_like(src)
+    capi.probe_copy(dst, src)
+    torch.cuda.synchronize()
+    assert torch.equal(dst, src)
+    assert capi.lib().pg_probe_tensor_peak(5, 10, None, None) == 1
