@@ -552,7 +552,6 @@ def main() -> None:
             line["reference_kernel_on_this_gpu"] = {"tflops": flops_step / (t_ref * 1e-3) / 1e12, "ms": t_ref,
                                                     "what": "reference mma.sync hgemm_peak compiled for sm_100a"}
         line["rmsnorm"] = rmsnorm_numbers(peaks, args.steps, args.warmup)
-        line["probe"] = probes()
         line["cpu_baseline"] = cpu_gemm_baseline()
     elif rank == 0 and world > 1:
         line["e2e"] = None
