@@ -300,6 +300,66 @@ def shape_sweep(peaks: dict) -> list:
     return rows
 
 
+def chain_sweep() -> list:
+    """RMSNorm -> projection at the LLM shapes of BASELINE config 3 (k = 4096 hidden size), four ways on one GPU:
+      two_op      rms_norm_fwd then gemm_peak (y written and re-read)
+      fused       rms_norm_rstd then gemm_peak_fused over the raw x (rstd applied in the epilogue)
+      fused_pdl   the same with the GEMM launched under programmatic stream serialisation (main loop overlaps
+                  the rstd kernel, only the epilogue waits)
+      torch       torch.nn.functional.rms_norm + F.linear (cuBLAS), the library comparator
+    Timing as in shape_sweep: weight sets rotated so that no weight is found in L2 from its previous use."""
+    import torch
+    import torch.nn.functional as F
+
+    import peakgemm_b200 as pg
+
+    rows = []
+    g = torch.Generator(device="cuda").manual_seed(5)
+    k = 4096
+    for m in (16, 128, 1024, 4096):
+        for n in (4096, 14336):
+            nbuf = max(2, min(16, -(-(256 << 20) // (2 * n * k))))
+            x = torch.randn(m, k, device="cuda", generator=g).to(torch.bfloat16)
+            gamma = (1 + 0.1 * torch.randn(k, device="cuda", generator=g)).float()
+            gamma16 = gamma.to(torch.bfloat16)
+            ws = [(0.02 * torch.randn(n, k, device="cuda", generator=g)).to(torch.bfloat16) for _ in range(nbuf)]
+            wfs = [pg.fold_gamma(w, gamma) for w in ws]
+            outs = [torch.empty(m, n, dtype=torch.bfloat16, device="cuda") for _ in range(nbuf)]
+            y = torch.empty_like(x)
+            rstd = torch.empty(m, device="cuda")
+            iters = 32
+
+            def loop(fn):
+                for i in range(4):
+                    fn(i % nbuf)
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for i in range(iters):
+                    fn(i % nbuf)
+                e1.record()
+                torch.cuda.synchronize()
+                return e0.elapsed_time(e1) / iters * 1e3
+
+            def two_op(i):
+                pg.rms_norm_fwd(y, x, gamma)
+                pg.gemm_peak(outs[i], y, ws[i])
+
+            def torch_chain(i):
+                torch.matmul(F.rms_norm(x, (k,), gamma16, 1e-6), ws[i].t(), out=outs[i])
+
+            t = {
+                "two_op_us": min(loop(two_op) for _ in range(3)),
+                "fused_us": min(loop(lambda i: pg.rms_norm_linear(outs[i], x, wfs[i], rstd=rstd, pdl=False)) for _ in range(3)),
+                "fused_pdl_us": min(loop(lambda i: pg.rms_norm_linear(outs[i], x, wfs[i], rstd=rstd, pdl=True)) for _ in range(3)),
+                "gemm_only_us": min(loop(lambda i: pg.gemm_peak(outs[i], x, ws[i])) for _ in range(3)),
+                "torch_us": min(loop(torch_chain) for _ in range(3)),
+            }
+            rows.append({"m": m, "n": n, "k": k, "weight_sets": nbuf, **t})
+            del ws, wfs, outs
+    return rows
+
+
 def config5(args) -> None:
     """BASELINE config 5: m = n = 32768, k = 16384 bf16, B column-sharded over the ranks (strong scaling),
     timed without a gather, with the all-gather (native shard-major result) and with the copy to row-major."""
@@ -380,6 +440,9 @@ def main() -> None:
     ap.add_argument("--probe", action="store_true", help="run only the roofline probes; prints one JSON object and exits")
     ap.add_argument("--sweep", action="store_true",
                     help="BASELINE configs 2 and 3 (every shape) against cuBLAS; prints one JSON object and exits")
+    ap.add_argument("--chain", action="store_true",
+                    help="RMSNorm -> projection chains (two operators, fused, fused + overlapped launch, torch); "
+                         "prints one JSON object and exits")
     ap.add_argument("--only-rmsnorm", type=int, default=0, metavar="ROWS",
                     help="profiling case: run only the RMSNorm kernels on [ROWS, 4096] and [ROWS, 8192] and exit")
     args = ap.parse_args()
@@ -415,6 +478,9 @@ def main() -> None:
         return
     if args.sweep:
         print(json.dumps({"sweep": shape_sweep(peaks), "peaks": {k: v for k, v in peaks.items() if not isinstance(v, dict)}}))
+        return
+    if args.chain:
+        print(json.dumps({"chain": chain_sweep()}))
         return
     if args.only_rmsnorm:
         print(json.dumps({"profiling_case": "rmsnorm", "rows": args.only_rmsnorm,

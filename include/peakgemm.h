@@ -103,6 +103,40 @@ int pg_hgemm_ex(void *c, const void *a, const void *b,
                 int dtype, int variant, int block_n, int max_sms, void *stream);
 
 /*
+ * pg_hgemm with a fused epilogue, every term optional (null pointer = absent):
+ *     d[i,j] = round_to_dtype(row_scale[i] * sum_k a[i,k] b[j,k] + bias[j] + residual[i,j])
+ * evaluated in fp32 from the fp32 accumulator with ONE rounding at the end (the
+ * unfused sequence rounds after the GEMM and again after each addition).
+ *   row_scale  [m] fp32.  With row_scale = the rstd of RMSNorm (pg_rmsnorm_rstd) and
+ *              gamma folded into the weights once (b[j,k] = w[j,k] * gamma[k]) this is
+ *              RMSNorm followed by the projection, without the normalised
+ *              activations ever being written or re-read
+ *   bias       [n] of `dtype`
+ *   residual   [m, n] of `dtype`, row pitch ldr (elements, % 8 == 0, >= n); may be d
+ *              itself with ldr == ldd (d += ...): every element is read by the thread
+ *              that produces it before it is stored.  Any other overlap of d with an
+ *              input is undefined
+ *   flags      PG_FUSED_PDL: launch with programmatic stream serialisation.  The
+ *              grid may start while the PREVIOUS kernel on `stream` is still
+ *              draining, and only the epilogue waits for it (griddepcontrol.wait)
+ *              before reading row_scale.  Set it only when that previous kernel is
+ *              the pg_rmsnorm_rstd call producing row_scale and a, b, bias,
+ *              residual were complete before that call was issued; ignored when
+ *              row_scale is null
+ * Same preconditions and kernels as pg_hgemm (the automatic choice between the
+ * persistent, split-K and skinny kernels; all three carry the epilogue).  k == 0
+ * is not accepted here (PG_ERR_UNSUPPORTED).  The reference's epilogue is a plain
+ * cast (src/impl/wmma_utils.h:101-112); it has no fused variant.
+ */
+#define PG_FUSED_PDL 1
+int pg_hgemm_fused(void *d, const void *a, const void *b,
+                   int64_t m, int64_t n, int64_t k,
+                   int64_t lda, int64_t ldb, int64_t ldd,
+                   const float *row_scale, const void *bias,
+                   const void *residual, int64_t ldr,
+                   int dtype, int flags, void *stream);
+
+/*
  * fp32 C[m,n] = A[m,k] * B[n,k]^T with true fp32 FMA accumulation (CUDA cores, no
  * TF32): the float branch of the gemm_peak operator, where the reference calls
  * sgemm::sgemm_peak (src/ops/gemm.cpp:34-43, src/impl/sgemm_impl.h:310-320) — by its
@@ -178,6 +212,16 @@ int pg_device_status(int *device_status, void *stream);
  */
 int pg_rmsnorm_fwd(void *y, const void *x, const float *gamma,
                    int64_t rows, int64_t h, float eps, int dtype, void *stream);
+
+/*
+ * rstd[r] = rsqrt(mean_j(x[r,j]^2) + eps), fp32, for the rows of x ([rows, h] of
+ * `dtype`, dense): the per-row scale pg_hgemm_fused applies (see there).  Reads x
+ * once; h % 8 == 0.  The kernel releases its stream dependents as soon as it
+ * starts, which only matters to a following launch that asks for programmatic
+ * serialisation (PG_FUSED_PDL).  No counterpart in the reference project.
+ */
+int pg_rmsnorm_rstd(float *rstd, const void *x, int64_t rows, int64_t h, float eps,
+                    int dtype, void *stream);
 
 /* Bytes of scratch pg_rmsnorm_bwd needs for this shape on the current device. */
 size_t pg_rmsnorm_bwd_workspace_bytes(int64_t rows, int64_t h);

@@ -175,6 +175,44 @@ def ulp_distance_16(out: torch.Tensor, ref_fp32: torch.Tensor) -> torch.Tensor:
     return (line(out) - line(ref)).abs()
 
 
+# ---------------------------------------------------- fused epilogue / chains ----
+# PARITY UNPINNED: the reference has no fused epilogue and no RMSNorm; these restate the definitions.
+
+def rmsnorm_rstd(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """rstd[r] = rsqrt(mean(x[r,:]^2) + eps), evaluated in float64, returned as float64."""
+    xd = x.double()
+    return torch.rsqrt(xd.pow(2).mean(dim=-1) + eps)
+
+
+def gemm_fused(a: torch.Tensor, b: torch.Tensor, row_scale=None, bias=None, residual=None) -> torch.Tensor:
+    """Unrounded fp32 row_scale[:,None] * (A @ B^T) + bias[None,:] + residual (absent terms skipped)."""
+    out = gemm_fp32(a, b).double()
+    if row_scale is not None:
+        out = out * row_scale.double()[:, None]
+    if bias is not None:
+        out = out + bias.double()[None, :]
+    if residual is not None:
+        out = out + residual.double()
+    return out.float()
+
+
+def gemm_fused_slack(a: torch.Tensor, b: torch.Tensor, row_scale=None) -> torch.Tensor:
+    """Per-element slack for a fp32 accumulation in another order: 2^-17 * |row_scale| * (|A| @ |B|^T).
+
+    The forward error of a length-k fp32 dot product is bounded by k * 2^-24 * sum|a_i b_i| and is
+    typically sqrt(k) * 2^-24 of it; 2^-17 covers k up to 16384 at the typical rate."""
+    s = torch.nn.functional.linear(a.float().abs(), b.float().abs()) * 2.0 ** -17
+    if row_scale is not None:
+        s = s * row_scale.float().abs()[:, None]
+    return s
+
+
+def rmsnorm_linear(x: torch.Tensor, gamma: torch.Tensor, w: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """Unrounded fp32 rms_norm(x; gamma) @ w^T by the definition (no folding, no intermediate rounding)."""
+    y = x.double() * rmsnorm_rstd(x, eps)[:, None] * gamma.double()[None, :]
+    return (y @ w.double().t()).float()
+
+
 # ------------------------------------------------------------ input generators ----
 # Seeded on the CPU so the oracle and the GPU see identical bits.
 

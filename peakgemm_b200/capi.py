@@ -23,6 +23,8 @@ SIGNATURES = {
     "pg_version": (ctypes.c_char_p, []),
     "pg_hgemm": (_i, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _p]),
     "pg_hgemm_ex": (_i, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _p]),
+    "pg_hgemm_fused": (_i, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _p, _p, _p, _i64, _i, _i, _p]),
+    "pg_rmsnorm_rstd": (_i, [_p, _p, _i64, _i64, ctypes.c_float, _i, _p]),
     "pg_hgemm_multi": (_i, [ctypes.POINTER(_p), _i, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _p]),
     "pg_peer_alloc": (_i, [_sz, ctypes.POINTER(_p), _p]),
     "pg_peer_open": (_i, [_p, ctypes.POINTER(_p)]),
@@ -98,6 +100,29 @@ def hgemm(c, a, b, *, variant: int = 0, block_n: int = 0, max_sms: int = 0, ldc:
                            b.stride(0) if n > 1 else k, ldc if ldc is not None else (c.stride(0) if m > 1 else n),
                            dtype_code(a.dtype), variant, block_n, max_sms, _stream_ptr(stream))
     check(st, "pg_hgemm_ex")
+
+
+PG_FUSED_PDL = 1
+
+
+def hgemm_fused(d, a, b, *, row_scale=None, bias=None, residual=None, pdl: bool = False, stream=None) -> None:
+    """pg_hgemm_fused: d = round(row_scale[:, None] * (a @ b^T) + bias[None, :] + residual), terms optional."""
+    m, k = a.shape
+    n = b.shape[0]
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    ldr = (residual.stride(0) if m > 1 else n) if residual is not None else 0
+    st = lib().pg_hgemm_fused(d.data_ptr(), a.data_ptr(), b.data_ptr(), m, n, k, a.stride(0) if m > 1 else k,
+                              b.stride(0) if n > 1 else k, d.stride(0) if m > 1 else n, ptr(row_scale), ptr(bias),
+                              ptr(residual), ldr, dtype_code(a.dtype), PG_FUSED_PDL if pdl else 0,
+                              _stream_ptr(stream))
+    check(st, "pg_hgemm_fused")
+
+
+def rmsnorm_rstd(rstd, x, eps: float = 1e-6, stream=None) -> None:
+    """pg_rmsnorm_rstd: rstd[r] = rsqrt(mean(x[r, :]^2) + eps), float32."""
+    rows, h = x.shape
+    check(lib().pg_rmsnorm_rstd(rstd.data_ptr(), x.data_ptr(), rows, h, eps, dtype_code(x.dtype),
+                                _stream_ptr(stream)), "pg_rmsnorm_rstd")
 
 
 def hgemm_multi(c_ptrs, a, b, ldc: int, n: int | None = None, *, max_sms: int = 0, stream=None) -> None:

@@ -99,6 +99,47 @@ int pg_hgemm_multi(void *const *c_list, int n_dst, const void *a, const void *b,
     return from_launch(r, e);
 }
 
+int pg_hgemm_fused(void *d, const void *a, const void *b, int64_t m, int64_t n, int64_t k, int64_t lda,
+                   int64_t ldb, int64_t ldd, const float *row_scale, const void *bias, const void *residual,
+                   int64_t ldr, int dtype, int flags, void *stream) {
+    if (m < 0 || n < 0 || k < 0) return PG_ERR_BAD_ARG;
+    if (dtype != PG_F16 && dtype != PG_BF16) return PG_ERR_BAD_ARG;
+    if (flags & ~PG_FUSED_PDL) return PG_ERR_BAD_ARG;
+    if (m == 0 || n == 0) return PG_OK;
+    if (k == 0) return PG_ERR_UNSUPPORTED;
+    if (!d || !a || !b) return PG_ERR_BAD_ARG;
+    if (lda < k || ldb < k || ldd < n) return PG_ERR_BAD_ARG;
+    if (residual && ldr < n) return PG_ERR_BAD_ARG;
+    if (n % 8 != 0 || k % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0 || ldd % 8 != 0) return PG_ERR_UNSUPPORTED;
+    if (residual && ldr % 8 != 0) return PG_ERR_UNSUPPORTED;
+    if (m > kMaxDim || n > kMaxDim || k > kMaxDim || (residual && ldr > kMaxDim)) return PG_ERR_UNSUPPORTED;
+    if (!aligned16(d) || !aligned16(a) || !aligned16(b)) return PG_ERR_MISALIGNED;
+    if ((bias && !aligned16(bias)) || (residual && !aligned16(residual)) ||
+        (row_scale && (reinterpret_cast<uintptr_t>(row_scale) & 3u)))
+        return PG_ERR_MISALIGNED;
+    pg::GemmArgs g{d, a, b, m, n, k, lda, ldb, ldd, dtype == PG_BF16};
+    g.row_scale = row_scale;
+    g.bias = bias;
+    g.residual = residual;
+    g.ldr = residual ? ldr : 0;
+    g.pdl_wait = (flags & PG_FUSED_PDL) != 0;
+    cudaError_t e = cudaSuccess;
+    const int r = pg::hgemm_launch(g, 0, 0, 0, static_cast<cudaStream_t>(stream), &e);
+    return from_launch(r, e);
+}
+
+int pg_rmsnorm_rstd(float *rstd, const void *x, int64_t rows, int64_t h, float eps, int dtype, void *stream) {
+    if (rows < 0 || h <= 0) return PG_ERR_BAD_ARG;
+    if (dtype != PG_F16 && dtype != PG_BF16) return PG_ERR_BAD_ARG;
+    if (rows == 0) return PG_OK;
+    if (!rstd || !x) return PG_ERR_BAD_ARG;
+    if (h % 8 != 0 || h > kMaxDim) return PG_ERR_UNSUPPORTED;
+    if (!aligned16(x) || (reinterpret_cast<uintptr_t>(rstd) & 3u)) return PG_ERR_MISALIGNED;
+    const cudaError_t e = pg::rmsnorm_rstd_launch(rstd, x, rows, h, eps, dtype == PG_BF16,
+                                                  static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? PG_OK : cuda_fail(e);
+}
+
 int pg_hgemm(void *c, const void *a, const void *b, int64_t m, int64_t n, int64_t k, int64_t lda,
              int64_t ldb, int64_t ldc, int dtype, void *stream) {
     return pg_hgemm_ex(c, a, b, m, n, k, lda, ldb, ldc, dtype, 0, 0, 0, stream);

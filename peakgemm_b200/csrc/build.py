@@ -28,7 +28,7 @@ INCLUDE = os.path.join(REPO_DIR, "include")
 DEVICE_LIB = os.path.join(PKG_DIR, "libPeakGemm_device.so")
 TORCH_LIB = os.path.join(PKG_DIR, "libPeakGemm.so")
 
-DEVICE_SOURCES = ["gemm_sm100.cu", "rmsnorm.cu", "rmsnorm_staged.cu", "rmsnorm_static.cu", "peer.cu", "sgemm.cu", "probes.cu", "api.cu"]
+DEVICE_SOURCES = ["gemm_sm100.cu", "rmsnorm.cu", "rmsnorm_staged.cu", "rmsnorm_static.cu", "rmsnorm_rstd.cu", "peer.cu", "sgemm.cu", "probes.cu", "api.cu"]
 DEVICE_HEADERS = ["ptx.cuh", "gemm_sm100.h", "rmsnorm.h", "sgemm.h", os.path.join(INCLUDE, "peakgemm.h")]
 
 NVCC_FLAGS = [

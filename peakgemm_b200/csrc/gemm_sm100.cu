@@ -125,6 +125,52 @@ struct DstMaps {
     CUtensorMap m[kMaxDst];
 };
 
+// Fused epilogue terms (all optional): out = row_scale[row] * acc + bias[col] + residual[row, col], one
+// rounding at the end.  The reference's epilogue is a plain cast (wmma_utils.h:101-112).
+struct EpiArgs {
+    const float *row_scale;     // [M] fp32 or null
+    const uint16_t *bias;       // [N] 16-bit or null
+    const uint16_t *residual;   // [M, ldr] 16-bit or null (may be the output itself: each element is read by the
+                                // thread that produces it, before that thread hands it to the store)
+    uint32_t ldr;
+    uint32_t pdl_wait;          // non-zero: griddepcontrol.wait before the first read of row_scale
+    __device__ __forceinline__ bool any() const { return row_scale || bias || residual; }
+};
+
+// Eight consecutive columns starting at `col` of row `row`: f[i] = f[i] * rs + bias + residual.
+template <bool BF16>
+__device__ __forceinline__ void epi_apply8(float (&f)[8], float rs, const EpiArgs &epi, bool row_ok, size_t row,
+                                           uint32_t col) {
+    float add[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) add[i] = 0.f;
+    if (epi.bias) {
+        const uint4 w = __ldg(reinterpret_cast<const uint4 *>(epi.bias + col));
+        float lo, hi;
+        unpack2<BF16>(w.x, lo, hi); add[0] = lo; add[1] = hi;
+        unpack2<BF16>(w.y, lo, hi); add[2] = lo; add[3] = hi;
+        unpack2<BF16>(w.z, lo, hi); add[4] = lo; add[5] = hi;
+        unpack2<BF16>(w.w, lo, hi); add[6] = lo; add[7] = hi;
+    }
+    if (epi.residual && row_ok) {
+        // plain load (not the read-only path): the residual may be the output buffer of this same kernel
+        const uint4 w = *reinterpret_cast<const uint4 *>(epi.residual + row * epi.ldr + col);
+        float lo, hi;
+        unpack2<BF16>(w.x, lo, hi); add[0] += lo; add[1] += hi;
+        unpack2<BF16>(w.y, lo, hi); add[2] += lo; add[3] += hi;
+        unpack2<BF16>(w.z, lo, hi); add[4] += lo; add[5] += hi;
+        unpack2<BF16>(w.w, lo, hi); add[6] += lo; add[7] += hi;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = fmaf(f[i], rs, add[i]);
+}
+
+__device__ __forceinline__ float epi_row_scale(const EpiArgs &epi, bool row_ok, size_t row) {
+    if (!epi.row_scale) return 1.f;
+    if (epi.pdl_wait) asm volatile("griddepcontrol.wait;" ::: "memory");
+    return row_ok ? *(epi.row_scale + row) : 1.f;
+}
+
 // Bounded mbarrier wait.  Returns false if the wait was abandoned.  The clock is
 // only consulted every 1024 failed probes (each probe already suspends the thread
 // for a hardware-defined interval), so the common short wait costs nothing extra.
@@ -166,7 +212,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                      const __grid_constant__ CUtensorMap tm_b,
                      const __grid_constant__ DstMaps tm_c, uint32_t n_dst,
-                     uint32_t M, uint32_t N, uint32_t K, uint32_t group_m, uint32_t flags, int *status) {
+                     uint32_t M, uint32_t N, uint32_t K, uint32_t group_m, uint32_t flags, const EpiArgs epi,
+                     int *status) {
     using C = Cfg<CTA_GROUP, BN, STAGES>;
     constexpr uint32_t kTileM = kBM * CTA_GROUP;
 
@@ -338,6 +385,9 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
             tc_fence_after_sync();
             const uint32_t row0 = mi * kTileM + rank * kBM + q * 32u;   // first row of this warp's slab
             const uint32_t taddr = tmem_base + acc * BN + ((q * 32u) << 16);
+            const bool fused = epi.any();
+            const bool row_ok = row0 + lane < M;
+            const float rs = fused ? epi_row_scale(epi, row_ok, row0 + lane) : 1.f;
 #pragma unroll 1
             for (uint32_t ch = 0; ch < BN / kStoreCols; ++ch) {
                 uint32_t v[2][32];
@@ -358,6 +408,20 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                 __syncwarp();
                 const uint32_t sbuf = buf0 + nbuf * kStageBufBytes;
                 uint8_t *sbuf_gen = buf0_gen + nbuf * kStageBufBytes;
+                const uint32_t col0 = ni * BN + ch * kStoreCols;
+                if (fused) {
+#pragma unroll
+                    for (uint32_t c = 0; c < 8; ++c) {
+                        if (col0 + c * 8u < N) {      // n is a multiple of 8: a group of 8 columns is in or out
+                            float f[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[c >> 2][(c & 3u) * 8u + i]);
+                            epi_apply8<BF16>(f, rs, epi, row_ok, row0 + lane, col0 + c * 8u);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) v[c >> 2][(c & 3u) * 8u + i] = __float_as_uint(f[i]);
+                        }
+                    }
+                }
                 // row `lane`, 8 chunks of 16 bytes, chunk c stored at position c ^ (row % 8)  (128-byte swizzle)
 #pragma unroll
                 for (uint32_t c = 0; c < 8; ++c) {
@@ -371,7 +435,6 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
-                const uint32_t col0 = ni * BN + ch * kStoreCols;
                 if (lane == 0) {
                     if (row0 < M && col0 < N) {
                         for (uint32_t d = 0; d < n_dst; ++d) {
@@ -439,7 +502,7 @@ struct SkCfg {
 template <int BN, int STAGES, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 hgemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                    uint16_t *__restrict__ c, uint32_t ldc, uint32_t M, uint32_t N, uint32_t K, int *status) {
+                    uint16_t *c, uint32_t ldc, uint32_t M, uint32_t N, uint32_t K, const EpiArgs epi, int *status) {
     using C = SkCfg<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -574,6 +637,8 @@ hgemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         const float *recv = reinterpret_cast<const float *>(smem_gen + C::kOffRecv);
         tc_fence_after_sync();
         const bool acc_ok = has_k && (*abort_flag == 0);
+        const bool fused = epi.any();
+        const float rs = fused ? epi_row_scale(epi, grow < M, grow) : 1.f;
 #pragma unroll 1
         for (uint32_t g = 0; g < W / 8; ++g) {
             uint32_t o[8];
@@ -596,6 +661,7 @@ hgemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             }
             const uint32_t gcol = ni * BN + rank * W + 8u * g;
             if (grow < M && gcol < N) {
+                if (fused) epi_apply8<BF16>(f, rs, epi, true, grow, gcol);
                 uint4 out;
                 out.x = pack2<BF16>(f[0], f[1]);
                 out.y = pack2<BF16>(f[2], f[3]);
@@ -645,7 +711,7 @@ struct SnCfg {
 template <int TOK, int STAGES, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 hgemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_constant__ CUtensorMap tm_w,
-                    uint16_t *__restrict__ c, uint32_t ldc, uint32_t M, uint32_t N, uint32_t K, int *status) {
+                    uint16_t *c, uint32_t ldc, uint32_t M, uint32_t N, uint32_t K, const EpiArgs epi, int *status) {
     using C = SnCfg<TOK, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -782,6 +848,25 @@ hgemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_con
             // C[mi, n] = D[n, mi]: for each token the 32 lanes of a warp write 32 consecutive columns of C
             const uint32_t n_glob = ni * kBM + row;
             if (n_glob < N) {
+                if (epi.any()) {
+                    // thread = one column of C: its bias once, then per token the row scale (one address for the
+                    // whole warp) and the residual element (32 consecutive columns per warp)
+                    float bias = 0.f, unused;
+                    if (epi.bias) unpack2<BF16>(static_cast<uint32_t>(epi.bias[n_glob]), bias, unused);
+                    if (epi.row_scale && epi.pdl_wait) asm volatile("griddepcontrol.wait;" ::: "memory");
+#pragma unroll
+                    for (uint32_t mi = 0; mi < TOK; ++mi) {
+                        if (mi < M) {
+                            float add = bias, r = 0.f;
+                            if (epi.residual)
+                                unpack2<BF16>(static_cast<uint32_t>(epi.residual[static_cast<size_t>(mi) * epi.ldr + n_glob]),
+                                              r, unused);
+                            add += r;
+                            const float rs = epi.row_scale ? epi.row_scale[mi] : 1.f;
+                            f[mi] = fmaf(f[mi], rs, add);
+                        }
+                    }
+                }
 #pragma unroll
                 for (uint32_t mi = 0; mi < TOK; ++mi) {
                     if (mi < M) {
@@ -921,6 +1006,30 @@ cudaError_t device_info(DeviceInfo **out) {
     return cudaSuccess;
 }
 
+EpiArgs make_epi(const GemmArgs &g) {
+    EpiArgs e;
+    e.row_scale = g.row_scale;
+    e.bias = static_cast<const uint16_t *>(g.bias);
+    e.residual = static_cast<const uint16_t *>(g.residual);
+    e.ldr = static_cast<uint32_t>(g.ldr);
+    e.pdl_wait = (g.pdl_wait && g.row_scale) ? 1u : 0u;
+    return e;
+}
+
+// Launch attributes common to the three kernels: the cluster shape, and for a caller that chained this
+// GEMM behind the kernel producing row_scale, programmatic stream serialisation (the grid may start
+// while that kernel drains; only the epilogue's griddepcontrol.wait orders the read of row_scale).
+int fill_attrs(cudaLaunchAttribute *attr, unsigned cluster_x, const GemmArgs &g) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster_x;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    if (!(g.pdl_wait && g.row_scale)) return 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    return 2;
+}
+
 template <int CTA_GROUP, int BN, int STAGES, bool BF16>
 cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t stream) {
     using C = Cfg<CTA_GROUP, BN, STAGES>;
@@ -956,13 +1065,9 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = C::kSmemBytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = CTA_GROUP;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attr[2];
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = fill_attrs(attr, CTA_GROUP, g);
     // Benchmark overrides, read once: PEAKGEMM_TUNE_GROUP_M (raster band height in tiles),
     // PEAKGEMM_TUNE_FLAGS (the kFlag* switches).
     static const int env_group_m = getenv("PEAKGEMM_TUNE_GROUP_M") ? atoi(getenv("PEAKGEMM_TUNE_GROUP_M")) : 0;
@@ -971,7 +1076,7 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
     const uint32_t flags = env_flags >= 0 ? static_cast<uint32_t>(env_flags) : kDefaultFlags;
     return cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b, tm_c, n_dst, static_cast<uint32_t>(g.m),
                               static_cast<uint32_t>(g.n), static_cast<uint32_t>(g.k), group_m, flags,
-                              d.status_word);
+                              make_epi(g), d.status_word);
 }
 
 template <int BN, int STAGES, bool BF16>
@@ -996,17 +1101,13 @@ cudaError_t launch_splitk(const GemmArgs &g, const DeviceInfo &d, int split, cud
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = C::kSmemBytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = split;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attr[2];
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = fill_attrs(attr, static_cast<unsigned>(split), g);
     (void)d;
     return cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b, static_cast<uint16_t *>(g.c), static_cast<uint32_t>(g.ldc),
                               static_cast<uint32_t>(g.m), static_cast<uint32_t>(g.n), static_cast<uint32_t>(g.k),
-                              d.status_word);
+                              make_epi(g), d.status_word);
 }
 
 template <int TOK, int STAGES, bool BF16>
@@ -1031,16 +1132,12 @@ cudaError_t launch_skinny(const GemmArgs &g, const DeviceInfo &d, int split, cud
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = C::kSmemBytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = split;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attr[2];
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = fill_attrs(attr, static_cast<unsigned>(split), g);
     return cudaLaunchKernelEx(&cfg, kernel, tm_tok, tm_w, static_cast<uint16_t *>(g.c), static_cast<uint32_t>(g.ldc),
                               static_cast<uint32_t>(g.m), static_cast<uint32_t>(g.n), static_cast<uint32_t>(g.k),
-                              d.status_word);
+                              make_epi(g), d.status_word);
 }
 
 // Cluster size for the skinny kernel: the largest S in {1,2,4,8} that keeps tiles * S within ~1.1 waves
@@ -1137,6 +1234,7 @@ int hgemm_launch(const GemmArgs &g, int variant, int block_n, int max_sms, cudaS
         }
     }
     if (g.n_extra_dst > 0 && variant > 2) return kLaunchBadConfig;
+    if (g.n_extra_dst > 0 && (g.row_scale || g.bias || g.residual)) return kLaunchBadConfig;
     static const int env_split = getenv("PEAKGEMM_TUNE_SPLITK") ? atoi(getenv("PEAKGEMM_TUNE_SPLITK")) : -1;
     // variant 4 = skinny kernel (m <= 64, operands swapped); the automatic choice for such m
     static const bool env_no_skinny = getenv("PEAKGEMM_TUNE_SKINNY") && getenv("PEAKGEMM_TUNE_SKINNY")[0] == '0';

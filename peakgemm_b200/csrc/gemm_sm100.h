@@ -14,6 +14,14 @@ struct GemmArgs {
     bool bf16;               // false: fp16
     int n_extra_dst = 0;     // further destinations of C (same extents and pitch as c), at most 7
     void *extra_dst[7] = {};
+    // Fused epilogue, every term optional (null = absent):
+    //   C[i,j] = round(row_scale[i] * sum_k A[i,k] B[j,k] + bias[j] + residual[i,j])
+    const float *row_scale = nullptr;   // [m] fp32
+    const void *bias = nullptr;         // [n], the matrices' element type
+    const void *residual = nullptr;     // [m, n] with row pitch ldr, the matrices' element type; may be c itself
+    int64_t ldr = 0;
+    bool pdl_wait = false;              // the epilogue waits for the preceding kernel of the stream before it reads
+                                        // row_scale (programmatic dependent launch); the main loop does not wait
 };
 
 enum LaunchResult { kLaunchOk = 0, kLaunchCuda = 1, kLaunchNotSm100 = 2, kLaunchBadConfig = 3 };

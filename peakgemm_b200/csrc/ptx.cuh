@@ -343,5 +343,18 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     }
 }
 
+// Two 16-bit values (low half first) -> two fp32, exact.
+template <bool BF16>
+__device__ __forceinline__ void unpack2(uint32_t w, float &lo, float &hi) {
+    if constexpr (BF16) {
+        lo = __uint_as_float(w << 16);
+        hi = __uint_as_float(w & 0xffff0000u);
+    } else {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w));
+        lo = f.x;
+        hi = f.y;
+    }
+}
+
 }  // namespace ptx
 }  // namespace pg

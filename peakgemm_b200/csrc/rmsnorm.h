@@ -35,6 +35,10 @@ cudaError_t rmsnorm_bwd_ctas(int64_t rows, int64_t h, bool bf16, int *ctas);
 cudaError_t rmsnorm_fwd_launch(const RmsFwdArgs &a, cudaStream_t stream);
 cudaError_t rmsnorm_bwd_launch(const RmsBwdArgs &a, int ctas, cudaStream_t stream);
 
+// rstd[r] = rsqrt(mean(x[r,:]^2) + eps), fp32 (rmsnorm_rstd.cu).
+cudaError_t rmsnorm_rstd_launch(float *rstd, const void *x, int64_t rows, int64_t h, float eps, bool bf16,
+                                cudaStream_t stream);
+
 // Bulk-copy staged variants (rmsnorm_staged.cu), used for 2048 <= h <= 16384.
 bool rmsnorm_staged_supported(int64_t h, bool bwd);
 cudaError_t rmsnorm_staged_ctas(int64_t rows, int64_t h, bool bwd, int *ctas, int *partial_rows);

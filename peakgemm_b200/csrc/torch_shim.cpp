@@ -14,6 +14,13 @@
 //
 // rms_norm_fwd / rms_norm_bwd have no counterpart in the reference; they follow
 // the same conventions: outputs first, caller-allocated, in place, return ().
+//
+// The reference's schema does not say that `c` is written (no `Tensor(a!)`), so a tracing
+// compiler sees an operator without outputs or side effects and may drop it.  The schema string
+// is kept verbatim for compatibility; next to it every operator has a twin `<name>_out` whose schema
+// marks the written tensors, registered for the CUDA key only (so fake/meta tracing never reaches the
+// kernels; the fake implementations live in the Python package).  gemm_peak_fused and rms_norm_rstd
+// (fused epilogue, RMSNorm folded into the projection) exist only in the annotated form.
 
 #include <ATen/ATen.h>
 #include <ATen/cuda/CUDAContext.h>
@@ -106,6 +113,77 @@ void rms_norm_bwd(Tensor &dx, Tensor &dgamma, Tensor &dy, Tensor &x, Tensor &gam
                  "rms_norm_bwd");
 }
 
+void gemm_peak_out(Tensor &c, const Tensor &a, const Tensor &b) {
+    TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && c.dim() == 2, "gemm_peak_out: a [m,k], b [n,k], c [m,n]");
+    Tensor a2 = a, b2 = b;
+    gemm_peak(c, a2, b2, a.size(0), b.size(0), a.size(1));
+}
+
+void rms_norm_fwd_out(Tensor &y, const Tensor &x, const Tensor &gamma, double eps) {
+    Tensor x2 = x, g2 = gamma;
+    rms_norm_fwd(y, x2, g2, eps);
+}
+
+void rms_norm_bwd_out(Tensor &dx, Tensor &dgamma, const Tensor &dy, const Tensor &x, const Tensor &gamma,
+                      double eps) {
+    Tensor dy2 = dy, x2 = x, g2 = gamma;
+    rms_norm_bwd(dx, dgamma, dy2, x2, g2, eps);
+}
+
+void rms_norm_rstd(Tensor &rstd, const Tensor &x, double eps) {
+    TORCH_CHECK(x.is_cuda() && rstd.is_cuda() && x.device() == rstd.device(), "rms_norm_rstd: CUDA tensors on one device");
+    TORCH_CHECK(x.is_contiguous() && rstd.is_contiguous() && x.dim() >= 1);
+    const int64_t h = x.size(-1);
+    const int64_t rows = h > 0 ? x.numel() / h : 0;
+    TORCH_CHECK(rstd.scalar_type() == at::kFloat && rstd.numel() == rows, "rms_norm_rstd: rstd must be float32 [rows]");
+    const int dt = dtype_code(x, "rms_norm_rstd");
+    c10::DeviceGuard device_guard(x.device());
+    auto stream = at::cuda::getCurrentCUDAStream();
+    check_status(pg_rmsnorm_rstd(rstd.data_ptr<float>(), x.data_ptr(), rows, h, static_cast<float>(eps), dt,
+                                 stream.stream()),
+                 "rms_norm_rstd");
+}
+
+// d[m,n] = row_scale[:,None] * (a[m,k] @ b[n,k]^T) + bias[None,:] + residual, each term optional.
+void gemm_peak_fused(Tensor &d, const Tensor &a, const Tensor &b, const std::optional<Tensor> &row_scale,
+                     const std::optional<Tensor> &bias, const std::optional<Tensor> &residual, bool pdl) {
+    TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && d.dim() == 2, "gemm_peak_fused: a [m,k], b [n,k], d [m,n]");
+    TORCH_CHECK(d.is_contiguous() && a.is_contiguous() && b.is_contiguous());
+    TORCH_CHECK(a.is_cuda() && b.is_cuda() && d.is_cuda() && a.device() == b.device() && a.device() == d.device(),
+                "gemm_peak_fused: tensors must be on one CUDA device");
+    TORCH_CHECK(a.scalar_type() == b.scalar_type() && a.scalar_type() == d.scalar_type(),
+                "gemm_peak_fused: a, b, d must have one dtype");
+    const int64_t m = a.size(0), k = a.size(1), n = b.size(0);
+    TORCH_CHECK(b.size(1) == k && d.size(0) == m && d.size(1) == n, "gemm_peak_fused: shapes do not match");
+    const float *rs = nullptr;
+    const void *bias_p = nullptr, *res_p = nullptr;
+    if (row_scale) {
+        TORCH_CHECK(row_scale->is_cuda() && row_scale->device() == a.device() && row_scale->is_contiguous() &&
+                        row_scale->scalar_type() == at::kFloat && row_scale->numel() == m,
+                    "gemm_peak_fused: row_scale must be float32 [m] on a's device");
+        rs = row_scale->data_ptr<float>();
+    }
+    if (bias) {
+        TORCH_CHECK(bias->is_cuda() && bias->device() == a.device() && bias->is_contiguous() &&
+                        bias->scalar_type() == a.scalar_type() && bias->numel() == n,
+                    "gemm_peak_fused: bias must be [n] of a's dtype on a's device");
+        bias_p = bias->data_ptr();
+    }
+    if (residual) {
+        TORCH_CHECK(residual->is_cuda() && residual->device() == a.device() && residual->is_contiguous() &&
+                        residual->scalar_type() == a.scalar_type() && residual->dim() == 2 &&
+                        residual->size(0) == m && residual->size(1) == n,
+                    "gemm_peak_fused: residual must be [m,n] of a's dtype on a's device");
+        res_p = residual->data_ptr();
+    }
+    const int dt = dtype_code(a, "gemm_peak_fused");
+    c10::DeviceGuard device_guard(a.device());
+    auto stream = at::cuda::getCurrentCUDAStream();
+    check_status(pg_hgemm_fused(d.data_ptr(), a.data_ptr(), b.data_ptr(), m, n, k, k, k, n, rs, bias_p, res_p, n, dt,
+                                pdl ? PG_FUSED_PDL : 0, stream.stream()),
+                 "gemm_peak_fused");
+}
+
 }  // namespace
 
 TORCH_LIBRARY(PeakGemm, m) {
@@ -115,4 +193,19 @@ TORCH_LIBRARY(PeakGemm, m) {
     m.impl("rms_norm_fwd", &rms_norm_fwd);
     m.def("rms_norm_bwd(Tensor dx, Tensor dgamma, Tensor dy, Tensor x, Tensor gamma, float eps) -> ()");
     m.impl("rms_norm_bwd", &rms_norm_bwd);
+    // annotated forms (see the note at the top of this file)
+    m.def("gemm_peak_out(Tensor(a!) c, Tensor a, Tensor b) -> ()");
+    m.def("rms_norm_fwd_out(Tensor(a!) y, Tensor x, Tensor gamma, float eps) -> ()");
+    m.def("rms_norm_bwd_out(Tensor(a!) dx, Tensor(b!) dgamma, Tensor dy, Tensor x, Tensor gamma, float eps) -> ()");
+    m.def("rms_norm_rstd(Tensor(a!) rstd, Tensor x, float eps) -> ()");
+    m.def("gemm_peak_fused(Tensor(a!) d, Tensor a, Tensor b, Tensor? row_scale, Tensor? bias, Tensor? residual, "
+          "bool pdl=False) -> ()");
+}
+
+TORCH_LIBRARY_IMPL(PeakGemm, CUDA, m) {
+    m.impl("gemm_peak_out", &gemm_peak_out);
+    m.impl("rms_norm_fwd_out", &rms_norm_fwd_out);
+    m.impl("rms_norm_bwd_out", &rms_norm_bwd_out);
+    m.impl("rms_norm_rstd", &rms_norm_rstd);
+    m.impl("gemm_peak_fused", &gemm_peak_fused);
 }

@@ -20,7 +20,7 @@ def declared_functions():
 
 def test_header_declares_the_expected_surface():
     names = declared_functions()
-    for must in ("pg_hgemm", "pg_hgemm_ex", "pg_hgemm_multi", "pg_sgemm", "pg_hgemm_config", "pg_rmsnorm_fwd", "pg_rmsnorm_bwd",
+    for must in ("pg_hgemm", "pg_hgemm_ex", "pg_hgemm_fused", "pg_rmsnorm_rstd", "pg_hgemm_multi", "pg_sgemm", "pg_hgemm_config", "pg_rmsnorm_fwd", "pg_rmsnorm_bwd",
                  "pg_rmsnorm_bwd_workspace_bytes", "pg_rmsnorm_bwd_static", "pg_device_status",
                  "pg_status_string", "pg_last_cuda_error", "pg_version", "pg_peer_alloc", "pg_peer_open",
                  "pg_peer_close", "pg_peer_free", "pg_probe_tensor_peak", "pg_probe_copy"):
@@ -79,6 +79,18 @@ def test_argument_checks_return_before_any_cuda_call():
     assert L.pg_rmsnorm_bwd_static(p, p, p, p, p, 4, 60, 1e-6, 1, None) == 3
     assert L.pg_rmsnorm_bwd_static(p, p, p, p, p, 4, 64, 1e-6, 9, None) == 1
     assert L.pg_device_status(None, None) == 1
+    fu = lambda *a: L.pg_hgemm_fused(*a)         # noqa: E731
+    assert fu(p, p, p, 0, 64, 64, 64, 64, 64, p, p, p, 64, 1, 0, None) == 0        # m == 0: no-op
+    assert fu(p, p, p, 64, 64, 0, 0, 0, 64, None, None, None, 0, 1, 0, None) == 3  # k == 0 not accepted here
+    assert fu(p, p, p, 64, 64, 64, 64, 64, 64, None, None, None, 0, 1, 2, None) == 1   # unknown flag
+    assert fu(p, p, p, 64, 64, 64, 64, 64, 64, None, None, p, 32, 1, 0, None) == 1     # ldr < n
+    assert fu(p, p, p, 64, 64, 64, 64, 64, 64, None, None, p, 68, 1, 0, None) == 3     # ldr % 8
+    assert fu(p, p, p, 64, 64, 64, 64, 64, 64, None, p + 2, None, 0, 1, 0, None) == 2  # bias misaligned
+    assert fu(p, p, p, 64, 64, 64, 64, 64, 64, p + 2, None, None, 0, 1, 0, None) == 2  # row_scale misaligned
+    assert fu(None, p, p, 64, 64, 64, 64, 64, 64, None, None, None, 0, 1, 0, None) == 1
+    assert L.pg_rmsnorm_rstd(p, p, 0, 64, 1e-6, 1, None) == 0
+    assert L.pg_rmsnorm_rstd(p, p, 4, 60, 1e-6, 1, None) == 3
+    assert L.pg_rmsnorm_rstd(None, p, 4, 64, 1e-6, 1, None) == 1
     assert capi.lib().pg_rmsnorm_bwd_workspace_bytes(0, 64) == 0
 
 
@@ -109,6 +121,45 @@ def test_torch_operator_schemas_match_the_reference():
         "PeakGemm::rms_norm_fwd(Tensor y, Tensor x, Tensor gamma, float eps) -> ()"
     assert str(torch.ops.PeakGemm.rms_norm_bwd.default._schema) == \
         "PeakGemm::rms_norm_bwd(Tensor dx, Tensor dgamma, Tensor dy, Tensor x, Tensor gamma, float eps) -> ()"
+
+
+def test_annotated_operators_trace_under_fake_tensors():
+    """The `_out` / fused operators mark what they write and have fake implementations, so a tracer can
+    run them without a GPU and without reaching the kernels (the reference's schema is un-annotated)."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    import peakgemm_b200 as pg
+
+    ops = torch.ops.PeakGemm
+    assert str(ops.gemm_peak_out.default._schema) == "PeakGemm::gemm_peak_out(Tensor(a!) c, Tensor a, Tensor b) -> ()"
+    assert "Tensor(a!) d" in str(ops.gemm_peak_fused.default._schema)
+    assert "Tensor(a!) dx, Tensor(b!) dgamma" in str(ops.rms_norm_bwd_out.default._schema)
+    for name in ("gemm_peak_out", "rms_norm_fwd_out", "rms_norm_bwd_out", "rms_norm_rstd", "gemm_peak_fused"):
+        assert getattr(ops, name).default._schema.is_mutable
+    with FakeTensorMode():
+        x = torch.empty(64, 128, dtype=torch.bfloat16, device="cuda")
+        w = torch.empty(32, 128, dtype=torch.bfloat16, device="cuda")
+        out = torch.empty(64, 32, dtype=torch.bfloat16, device="cuda")
+        gamma = torch.empty(128, device="cuda")
+        rstd = pg.rms_norm_linear(out, x, w, bias=torch.empty(32, dtype=torch.bfloat16, device="cuda"), residual=out)
+        assert rstd.shape == (64,) and rstd.dtype == torch.float32
+        ops.gemm_peak_out(out, x, w)
+        ops.rms_norm_fwd_out(x.clone(), x, gamma, 1e-6)
+        ops.rms_norm_bwd_out(torch.empty_like(x), torch.empty_like(gamma), x, x, gamma, 1e-6)
+    # no CPU fallback behind the CUDA-only registrations either
+    with pytest.raises((RuntimeError, NotImplementedError)):
+        ops.gemm_peak_out(torch.zeros(8, 8, dtype=torch.bfloat16), torch.zeros(8, 8, dtype=torch.bfloat16),
+                          torch.zeros(8, 8, dtype=torch.bfloat16))
+
+
+def test_fold_gamma_is_the_rounded_product():
+    import peakgemm_b200 as pg
+
+    g = torch.Generator().manual_seed(3)
+    w = torch.randn(24, 64, generator=g).to(torch.bfloat16)
+    gamma = 1 + 0.1 * torch.randn(64, generator=g)
+    wf = pg.fold_gamma(w, gamma)
+    assert wf.dtype == w.dtype and torch.equal(wf, (w.float() * gamma[None, :]).to(torch.bfloat16))
 
 
 def test_python_surface_mirrors_the_reference_wrapper():
