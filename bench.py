@@ -307,7 +307,9 @@ def chain_sweep() -> list:
       fused_pdl   the same with the GEMM launched under programmatic stream serialisation (main loop overlaps
                   the rstd kernel, only the epilogue waits)
       torch       torch.nn.functional.rms_norm + F.linear (cuBLAS), the library comparator
-    Timing as in shape_sweep: weight sets rotated so that no weight is found in L2 from its previous use."""
+    plus the GEMM, the norm and the rstd kernel alone.  Weight sets are rotated so that no weight is found in L2
+    from its previous use.  Each case is timed twice: 32 chains captured in one CUDA graph and replayed (device
+    time) and launched eagerly from Python (adds the host cost of two operator calls per chain)."""
     import torch
     import torch.nn.functional as F
 
@@ -330,6 +332,8 @@ def chain_sweep() -> list:
             iters = 32
 
             def loop(fn):
+                """(graph, eager) us per chain: `iters` chains captured in one CUDA graph and replayed (device
+                time, no host launch cost), and the same chains launched eagerly from Python."""
                 for i in range(4):
                     fn(i % nbuf)
                 torch.cuda.synchronize()
@@ -339,7 +343,19 @@ def chain_sweep() -> list:
                     fn(i % nbuf)
                 e1.record()
                 torch.cuda.synchronize()
-                return e0.elapsed_time(e1) / iters * 1e3
+                eager = e0.elapsed_time(e1) / iters * 1e3
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    for i in range(iters):
+                        fn(i % nbuf)
+                best = float("inf")
+                for _ in range(4):                    # the first replay is the warm-up
+                    e0.record()
+                    graph.replay()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    best = min(best, e0.elapsed_time(e1) / iters * 1e3)
+                return best, eager
 
             def two_op(i):
                 pg.rms_norm_fwd(y, x, gamma)
@@ -348,13 +364,18 @@ def chain_sweep() -> list:
             def torch_chain(i):
                 torch.matmul(F.rms_norm(x, (k,), gamma16, 1e-6), ws[i].t(), out=outs[i])
 
-            t = {
-                "two_op_us": min(loop(two_op) for _ in range(3)),
-                "fused_us": min(loop(lambda i: pg.rms_norm_linear(outs[i], x, wfs[i], rstd=rstd, pdl=False)) for _ in range(3)),
-                "fused_pdl_us": min(loop(lambda i: pg.rms_norm_linear(outs[i], x, wfs[i], rstd=rstd, pdl=True)) for _ in range(3)),
-                "gemm_only_us": min(loop(lambda i: pg.gemm_peak(outs[i], x, ws[i])) for _ in range(3)),
-                "torch_us": min(loop(torch_chain) for _ in range(3)),
+            cases = {
+                "two_op": two_op,
+                "fused": lambda i: pg.rms_norm_linear(outs[i], x, wfs[i], rstd=rstd, pdl=False),
+                "fused_pdl": lambda i: pg.rms_norm_linear(outs[i], x, wfs[i], rstd=rstd, pdl=True),
+                "gemm_only": lambda i: pg.gemm_peak(outs[i], x, ws[i]),
+                "norm_only": lambda i: pg.rms_norm_fwd(y, x, gamma),
+                "rstd_only": lambda i: torch.ops.PeakGemm.rms_norm_rstd(rstd, x, 1e-6),
+                "torch": torch_chain,
             }
+            t = {}
+            for name, fn in cases.items():
+                t[f"{name}_us"], t[f"{name}_eager_us"] = loop(fn)
             rows.append({"m": m, "n": n, "k": k, "weight_sets": nbuf, **t})
             del ws, wfs, outs
     return rows
