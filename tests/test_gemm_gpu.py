@@ -191,6 +191,19 @@ def test_multi_destination_epilogue(cuda):
     for f in fulls[1:]:
         assert torch.equal(f[:, 512:512 + n], fulls[0][:, 512:512 + n])
     assert torch.equal(fulls[1][:, :512], before[:, :512]) and torch.equal(fulls[1][:, 1024:], before[:, 1024:])
+    # enough tiles for the 256-wide CTA-pair kernel, several tiles per CTA pair (the staging boxes are reused
+    # across tiles while stores to three destinations are in flight), tails in m and n
+    m3, n3, k3 = 4000, 4104, 320
+    a3, b3 = oracle.gemm_inputs_uniform(m3, n3, k3, BF16, 14)
+    outs3 = [helpers.garbage_like((m3, n3), BF16, "cuda") for _ in range(3)]
+    capi.hgemm_multi([o.data_ptr() for o in outs3], a3.cuda(), b3.cuda(), ldc=n3)
+    single = helpers.garbage_like((m3, n3), BF16, "cuda")
+    capi.hgemm(single, a3.cuda(), b3.cuda())
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0
+    helpers.check_gemm(outs3[0], a3, b3, exact_rows=False)
+    for o in outs3:
+        assert torch.equal(o, single)
     # a small-m case takes the one-CTA kernel
     a2, b2 = oracle.gemm_inputs_uniform(48, 256, 512, F16, 13)
     outs = [helpers.garbage_like((48, 256), F16, "cuda") for _ in range(2)]
