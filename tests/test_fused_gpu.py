@@ -187,6 +187,30 @@ def test_overlapped_launch_never_reads_stale_row_scales(cuda):
         assert torch.equal(o.view(torch.int16), ref.view(torch.int16))
 
 
+@pytest.mark.parametrize("m,n,k", [(16, 4096, 1024), (128, 4096, 4096), (512, 1024, 512)])
+def test_overlapped_launch_flag_without_a_producer_kernel(cuda, m, n, k):
+    """PG_FUSED_PDL on an idle stream, or behind a kernel that never releases its dependents early, degrades to
+    an ordinary launch: same bits as without the flag, on the skinny, split-K and persistent kernels."""
+    from peakgemm_b200 import capi
+
+    a, b, rs, _, _ = fused_inputs(m, n, k, BF16, 41)
+    ad, bd, rsd = a.cuda(), b.cuda(), rs.cuda()
+    plain = helpers.garbage_like((m, n), BF16, "cuda")
+    idle = helpers.garbage_like((m, n), BF16, "cuda")
+    behind = helpers.garbage_like((m, n), BF16, "cuda")
+    capi.hgemm_fused(plain, ad, bd, row_scale=rsd)
+    torch.cuda.synchronize()
+    capi.hgemm_fused(idle, ad, bd, row_scale=rsd, pdl=True)
+    torch.cuda.synchronize()
+    rsd2 = torch.zeros_like(rsd)
+    rsd2.copy_(rsd)                                   # an ordinary kernel writes the scales just before
+    capi.hgemm_fused(behind, ad, bd, row_scale=rsd2, pdl=True)
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0
+    assert torch.equal(plain.view(torch.int16), idle.view(torch.int16))
+    assert torch.equal(plain.view(torch.int16), behind.view(torch.int16))
+
+
 @pytest.mark.parametrize("pdl", [False, True])
 def test_cuda_graph_replay_of_norm_gemm_chains(cuda, pdl):
     """Both chains are capturable (no allocation, no synchronisation, nothing host-side per call that
