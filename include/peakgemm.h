@@ -103,6 +103,25 @@ int pg_hgemm_ex(void *c, const void *a, const void *b,
                 int dtype, int variant, int block_n, int max_sms, void *stream);
 
 /*
+ * pg_hgemm with an optional scratch buffer that lets the kernel split the LAST, partial wave of output
+ * tiles: when the tiles do not fill a whole number of waves of the persistent grid and the remainder
+ * occupies at most half of the SM pairs and k is long enough for the exchange to pay (about k >= 8192), each
+ * remainder tile is cut into 2-8 slices of k that run on the otherwise idle SM pairs; the slices' fp32 partial sums pass through `workspace` and are added in slice
+ * order (deterministic) before the one rounding.  Results differ from pg_hgemm only by the fp32 summation
+ * order of those tiles.  pg_hgemm_workspace_bytes(m, n, k) gives the size that enables the split on the
+ * current device (0: this shape would not be split; then workspace may be NULL).  A smaller or NULL
+ * workspace simply disables the split.  workspace: 256-byte aligned device memory, private to this call until
+ * the kernel has finished (two calls that overlap on the GPU need two buffers); it needs no
+ * initialisation (the call clears the flag words it uses with one cudaMemsetAsync on `stream`).
+ * The reference has no counterpart: it launches one CTA per tile (get_grid, hgemm_wmma_impl.h:373-378).
+ */
+size_t pg_hgemm_workspace_bytes(int64_t m, int64_t n, int64_t k);
+int pg_hgemm_ws(void *c, const void *a, const void *b,
+                int64_t m, int64_t n, int64_t k,
+                int64_t lda, int64_t ldb, int64_t ldc,
+                int dtype, void *workspace, size_t workspace_bytes, void *stream);
+
+/*
  * pg_hgemm with a fused epilogue, every term optional (null pointer = absent):
  *     d[i,j] = round_to_dtype(row_scale[i] * sum_k a[i,k] b[j,k] + bias[j] + residual[i,j])
  * evaluated in fp32 from the fp32 accumulator with ONE rounding at the end (the

@@ -23,6 +23,8 @@ SIGNATURES = {
     "pg_version": (ctypes.c_char_p, []),
     "pg_hgemm": (_i, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _p]),
     "pg_hgemm_ex": (_i, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _p]),
+    "pg_hgemm_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "pg_hgemm_ws": (_i, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _p, _sz, _p]),
     "pg_hgemm_fused": (_i, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _p, _p, _p, _i64, _i, _i, _p]),
     "pg_rmsnorm_rstd": (_i, [_p, _p, _i64, _i64, ctypes.c_float, _i, _p]),
     "pg_hgemm_multi": (_i, [ctypes.POINTER(_p), _i, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _p]),
@@ -100,6 +102,23 @@ def hgemm(c, a, b, *, variant: int = 0, block_n: int = 0, max_sms: int = 0, ldc:
                            b.stride(0) if n > 1 else k, ldc if ldc is not None else (c.stride(0) if m > 1 else n),
                            dtype_code(a.dtype), variant, block_n, max_sms, _stream_ptr(stream))
     check(st, "pg_hgemm_ex")
+
+
+def hgemm_workspace_bytes(m: int, n: int, k: int) -> int:
+    """Bytes of scratch with which pg_hgemm_ws splits the last partial wave of this shape (0: it would not)."""
+    return int(lib().pg_hgemm_workspace_bytes(m, n, k))
+
+
+def hgemm_ws(c, a, b, workspace=None, stream=None) -> None:
+    """pg_hgemm_ws: C = A @ B^T, with `workspace` (a uint8 CUDA tensor or None) enabling the tail split."""
+    m, k = a.shape
+    n = b.shape[0]
+    st = lib().pg_hgemm_ws(c.data_ptr(), a.data_ptr(), b.data_ptr(), m, n, k, a.stride(0) if m > 1 else k,
+                           b.stride(0) if n > 1 else k, c.stride(0) if m > 1 else n, dtype_code(a.dtype),
+                           workspace.data_ptr() if workspace is not None else None,
+                           workspace.numel() * workspace.element_size() if workspace is not None else 0,
+                           _stream_ptr(stream))
+    check(st, "pg_hgemm_ws")
 
 
 PG_FUSED_PDL = 1

@@ -75,6 +75,44 @@ int pg_hgemm_ex(void *c, const void *a, const void *b, int64_t m, int64_t n, int
     return from_launch(r, e);
 }
 
+size_t pg_hgemm_workspace_bytes(int64_t m, int64_t n, int64_t k) {
+    if (m <= 0 || n <= 0 || k <= 0) return 0;
+    static int sm_count[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        cudaGetLastError();
+        return 0;
+    }
+    if (sm_count[dev] == 0) {
+        int n_sm = 0;
+        if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+            cudaGetLastError();
+            return 0;
+        }
+        sm_count[dev] = n_sm;
+    }
+    return pg::hgemm_workspace_bytes(m, n, k, sm_count[dev]);
+}
+
+int pg_hgemm_ws(void *c, const void *a, const void *b, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb,
+                int64_t ldc, int dtype, void *workspace, size_t workspace_bytes, void *stream) {
+    if (m < 0 || n < 0 || k < 0) return PG_ERR_BAD_ARG;
+    if (dtype != PG_F16 && dtype != PG_BF16) return PG_ERR_BAD_ARG;
+    if (m == 0 || n == 0) return PG_OK;
+    if (!c || (k > 0 && (!a || !b))) return PG_ERR_BAD_ARG;
+    if (lda < k || ldb < k || ldc < n) return PG_ERR_BAD_ARG;
+    if (n % 8 != 0 || k % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0 || ldc % 8 != 0) return PG_ERR_UNSUPPORTED;
+    if (m > kMaxDim || n > kMaxDim || k > kMaxDim) return PG_ERR_UNSUPPORTED;
+    if (!aligned16(c) || (k > 0 && (!aligned16(a) || !aligned16(b)))) return PG_ERR_MISALIGNED;
+    if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 255u)) return PG_ERR_MISALIGNED;
+    pg::GemmArgs g{c, a, b, m, n, k, lda, ldb, ldc, dtype == PG_BF16};
+    g.workspace = workspace_bytes ? workspace : nullptr;
+    g.workspace_bytes = workspace ? workspace_bytes : 0;
+    cudaError_t e = cudaSuccess;
+    const int r = pg::hgemm_launch(g, 0, 0, 0, static_cast<cudaStream_t>(stream), &e);
+    return from_launch(r, e);
+}
+
 int pg_hgemm_multi(void *const *c_list, int n_dst, const void *a, const void *b, int64_t m, int64_t n, int64_t k,
                    int64_t lda, int64_t ldb, int64_t ldc, int dtype, int max_sms, void *stream) {
     if (!c_list || n_dst < 1 || n_dst > 8) return PG_ERR_BAD_ARG;

@@ -88,6 +88,7 @@ enum : int {
     kStMmaFull = 2,
     kStMmaAccEmpty = 3,
     kStEpiAccFull = 4,
+    kStEpiTailFlag = 5,
 };
 
 template <int CTA_GROUP, int BN, int STAGES>
@@ -207,13 +208,91 @@ __device__ __forceinline__ void tile_coords(uint32_t kGroupM, uint32_t t, uint32
     if (serpentine && (band & 1u)) ni = n_tiles - 1 - ni;
 }
 
+// Tail split.  With T tiles on W workers the last, partial wave keeps only T mod W workers busy for a whole
+// tile time.  When that remainder is at most W/2, the remainder tiles are cut into `split` k-slices and handed to
+// `split` workers each: slice 0 (the owner) keeps the tile, slices 1.. (helpers) write their fp32 partial
+// accumulators to a caller-provided workspace and raise a flag; the owner's epilogue adds the partials in slice
+// order (deterministic) before it rounds.  Helpers never wait for anybody and every worker runs its whole tiles
+// first, so an owner only ever waits for work that is already running; its wait is bounded like every other.
+//   full_tiles  tiles [0, full_tiles) are walked whole, worker-strided; a multiple of the worker count when
+//               split >= 2, the tile count otherwise
+//   split       0: no split; >= 2: k-slices per remainder tile (remainder * split <= workers)
+//   ws          [remainder][split-1][CTA of the pair][BN/4][128 rows][4] fp32
+//   flags       [remainder][split-1][CTA of the pair][epilogue warp], zero at launch
+struct TailArgs {
+    uint32_t full_tiles;
+    uint32_t split;
+    float *ws;
+    uint32_t *flags;
+};
+
+struct Unit {
+    uint32_t tile, kb0, kb1, slice, tail_idx;
+    bool valid, is_tail;
+};
+
+// The i-th piece of work of `worker`: its whole tiles first, then at most one k-slice of a remainder tile.
+__device__ __forceinline__ Unit unit_at(uint32_t i, uint32_t worker, uint32_t workers, uint32_t total_tiles,
+                                        uint32_t k_blocks, const TailArgs &tail) {
+    Unit u;
+    u.kb0 = 0;
+    u.kb1 = k_blocks;
+    u.slice = 0;
+    u.tail_idx = 0;
+    u.is_tail = false;
+    u.tile = worker + i * workers;
+    u.valid = u.tile < tail.full_tiles;
+    if (!u.valid && tail.split >= 2 && i == tail.full_tiles / workers) {
+        const uint32_t rem = total_tiles - tail.full_tiles;
+        if (worker < rem * tail.split) {
+            u.tail_idx = worker / tail.split;
+            u.slice = worker - u.tail_idx * tail.split;
+            u.tile = tail.full_tiles + u.tail_idx;
+            const uint32_t per = (k_blocks + tail.split - 1) / tail.split;
+            u.kb0 = min(k_blocks, u.slice * per);
+            u.kb1 = min(k_blocks, u.kb0 + per);
+            u.valid = true;
+            u.is_tail = true;
+        }
+    }
+    return u;
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Bounded wait for a helper's flag.  Returns false if the wait was abandoned.
+__device__ __forceinline__ bool wait_flag(const uint32_t *flag, const WaitCtx &ctx) {
+    uint64_t t0 = 0;
+    uint32_t spins = 0;
+    while (ld_acquire_gpu(flag) == 0u) {
+        if ((++spins & 255u) == 0) {
+            if (*ctx.abort_flag) return false;
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitTimeoutNs) {
+                *ctx.abort_flag = 1;
+                atomicCAS(ctx.status, 0, static_cast<int>(kStEpiTailFlag));
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
 template <int CTA_GROUP, int BN, int STAGES, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                      const __grid_constant__ CUtensorMap tm_b,
                      const __grid_constant__ DstMaps tm_c, uint32_t n_dst,
                      uint32_t M, uint32_t N, uint32_t K, uint32_t group_m, uint32_t flags, const EpiArgs epi,
-                     int *status) {
+                     const TailArgs tail, int *status) {
     using C = Cfg<CTA_GROUP, BN, STAGES>;
     constexpr uint32_t kTileM = kBM * CTA_GROUP;
 
@@ -285,12 +364,14 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
             const bool hint_b = (flags & (kFlagBEvictFirst | kFlagBEvictLast)) != 0;
             const uint64_t pol_a = l2_policy_evict_last();
             const uint64_t pol_b = (flags & kFlagBEvictFirst) ? l2_policy_evict_first() : l2_policy_evict_last();
-            for (uint32_t t = worker; ok && t < total_tiles; t += workers) {
+            for (uint32_t it = 0; ok; ++it) {
+                const Unit u = unit_at(it, worker, workers, total_tiles, k_blocks, tail);
+                if (!u.valid) break;
                 uint32_t mi, ni;
-                tile_coords(group_m, t, m_tiles, n_tiles, mi, ni, (flags & kFlagSerpentine) != 0);
+                tile_coords(group_m, u.tile, m_tiles, n_tiles, mi, ni, (flags & kFlagSerpentine) != 0);
                 const int32_t row_a = static_cast<int32_t>(mi * kTileM + rank * kBM);
                 const int32_t row_b = static_cast<int32_t>(ni * BN + rank * C::kBRows);
-                for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+                for (uint32_t kb = u.kb0; kb < u.kb1; ++kb) {
                     if (leader) {
                         // wait until the MMAs that read this stage have completed
                         ok = wait_bar(bar_empty + stage * 8, phase ^ 1u, ctx, kStProducerEmpty);
@@ -334,13 +415,15 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
             constexpr uint32_t idesc = instr_desc_f16(BF16, kBM * CTA_GROUP, BN);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
-            for (uint32_t t = worker; ok && t < total_tiles; t += workers) {
+            for (uint32_t it = 0; ok; ++it) {
+                const Unit u = unit_at(it, worker, workers, total_tiles, k_blocks, tail);
+                if (!u.valid) break;
                 // the epilogue must have drained this accumulator (passes at once the first two times)
                 ok = wait_bar(bar_acc_empty + acc * 8, acc_phase ^ 1u, ctx, kStMmaAccEmpty);
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t tmem_d = tmem_base + acc * BN;
-                for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+                for (uint32_t kb = u.kb0; kb < u.kb1; ++kb) {
                     ok = wait_bar(bar_full + stage * 8, phase, ctx, kStMmaFull);
                     if (!ok) break;
                     tc_fence_after_sync();
@@ -349,7 +432,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
 #pragma unroll
                     for (uint32_t k = 0; k < kBK / kUmmaK; ++k) {
                         // 16 elements of k = 32 bytes inside the 128-byte swizzle row = +2 in the >>4 address field
-                        umma_f16<CTA_GROUP>(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0u ? 1u : 0u);
+                        umma_f16<CTA_GROUP>(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb != u.kb0 || k != 0u) ? 1u : 0u);
                     }
                     umma_commit<CTA_GROUP>(bar_empty + stage * 8);   // stage free once these MMAs are done
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -371,9 +454,11 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         uint32_t acc = 0, acc_phase = 0, nbuf = 0;
         bool ok = true;
         const uint64_t pol_store = l2_policy_evict_first();
-        for (uint32_t t = worker; ok && t < total_tiles; t += workers) {
+        for (uint32_t it = 0; ok; ++it) {
+            const Unit u = unit_at(it, worker, workers, total_tiles, k_blocks, tail);
+            if (!u.valid) break;
             uint32_t mi, ni;
-            tile_coords(group_m, t, m_tiles, n_tiles, mi, ni, (flags & kFlagSerpentine) != 0);
+            tile_coords(group_m, u.tile, m_tiles, n_tiles, mi, ni, (flags & kFlagSerpentine) != 0);
             // All 32 lanes probe: a failed try_wait parks the warp in hardware, so this costs nothing (a
             // one-lane poll with __nanosleep back-off executed 40 % MORE instructions and ran 0.7 % slower).
             ok = wait_bar(bar_acc_full + acc * 8, acc_phase, ctx, kStEpiAccFull);
@@ -388,6 +473,46 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
             const bool fused = epi.any();
             const bool row_ok = row0 + lane < M;
             const float rs = fused ? epi_row_scale(epi, row_ok, row0 + lane) : 1.f;
+            // k-slices of a remainder tile: where this warp's rows of slice j live in the workspace, and its flag
+            constexpr uint32_t kPartFloats = kBM * BN;                  // one CTA's partial tile
+            const uint32_t n_parts = (u.is_tail && u.slice == 0) ? tail.split - 1u : 0u;
+            const uint32_t part0 = (u.tail_idx * (tail.split - 1u)) * CTA_GROUP + rank;   // slice 1 of this tile
+            if (u.is_tail && u.slice > 0) {
+                // ===== helper: fp32 partial sums to the workspace, then the flag =====
+                const uint32_t part = part0 + (u.slice - 1u) * CTA_GROUP;
+                float4 *dst = reinterpret_cast<float4 *>(tail.ws + static_cast<size_t>(part) * kPartFloats) +
+                              (q * 32u + lane);
+#pragma unroll 1
+                for (uint32_t ch = 0; ch < BN / kStoreCols; ++ch) {
+                    uint32_t v[2][32];
+                    tmem_ld_32x32b_x32(taddr + ch * kStoreCols, v[0]);
+                    tmem_ld_32x32b_x32(taddr + ch * kStoreCols + 32u, v[1]);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (uint32_t c4 = 0; c4 < 16; ++c4) {      // column group c4 of this chunk: [group][row][4]
+                        const uint32_t *src = &v[c4 >> 3][(c4 & 7u) * 4u];
+                        dst[(ch * 16u + c4) * kBM] = make_float4(__uint_as_float(src[0]), __uint_as_float(src[1]),
+                                                                 __uint_as_float(src[2]), __uint_as_float(src[3]));
+                    }
+                }
+                tc_fence_before_sync();
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) {
+                    if constexpr (CTA_GROUP == 2) mbar_arrive_cluster(acc_empty_leader + acc * 8);
+                    else mbar_arrive(bar_acc_empty + acc * 8);
+                    st_release_gpu(tail.flags + part * kEpiWarps + e, 1u);
+                }
+                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+                continue;
+            }
+            if (n_parts) {
+                // ===== owner: the helpers' partial sums must have landed =====
+                for (uint32_t j = 0; ok && j < n_parts; ++j)
+                    ok = wait_flag(tail.flags + (part0 + j * CTA_GROUP) * kEpiWarps + e, ctx);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+            }
 #pragma unroll 1
             for (uint32_t ch = 0; ch < BN / kStoreCols; ++ch) {
                 uint32_t v[2][32];
@@ -401,6 +526,20 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                     if (lane == 0) {
                         if constexpr (CTA_GROUP == 2) mbar_arrive_cluster(acc_empty_leader + acc * 8);
                         else mbar_arrive(bar_acc_empty + acc * 8);
+                    }
+                }
+                for (uint32_t j = 0; j < n_parts; ++j) {      // slice order: deterministic
+                    const float4 *src = reinterpret_cast<const float4 *>(
+                                            tail.ws + static_cast<size_t>(part0 + j * CTA_GROUP) * kPartFloats) +
+                                        (q * 32u + lane);
+#pragma unroll
+                    for (uint32_t c4 = 0; c4 < 16; ++c4) {
+                        const float4 p = __ldcg(src + (ch * 16u + c4) * kBM);
+                        uint32_t *d = &v[c4 >> 3][(c4 & 7u) * 4u];
+                        d[0] = __float_as_uint(__uint_as_float(d[0]) + p.x);
+                        d[1] = __float_as_uint(__uint_as_float(d[1]) + p.y);
+                        d[2] = __float_as_uint(__uint_as_float(d[2]) + p.z);
+                        d[3] = __float_as_uint(__uint_as_float(d[3]) + p.w);
                     }
                 }
                 // the store issued two chunks ago from this buffer must have finished reading it
@@ -1030,6 +1169,44 @@ int fill_attrs(cudaLaunchAttribute *attr, unsigned cluster_x, const GemmArgs &g)
     return 2;
 }
 
+}  // namespace
+
+// Tail split plan for the 256-wide CTA-pair kernel on `workers` SM pairs: k-slices per remainder tile (0 = none)
+// and the workspace it needs.  The remainder must be at most half a wave, and the split must pay: the owner of a
+// tile reads its helpers' partial sums one after the other (about 3 us each, L2 latency bound), and a remainder
+// wave on a mostly idle, un-throttled GPU runs at about 0.75 of a tile time anyway.  Measured on B200
+// (1024 x 14336 x k): k = 4096 no gain with any slice count, k = 16384 455 -> 365 us with 8 slices.  So the slice
+// count minimises  tile/s + 3.2 (s - 1) + 4 us  (tile = 0.38 us per k-block) and the split is used only when that
+// is under 0.6 of a tile time.
+void plan_tail(int64_t m, int64_t n, int64_t k, int workers, uint32_t *full_tiles, uint32_t *split, size_t *bytes) {
+    const int64_t tiles = ((m + 255) / 256) * ((n + 255) / 256);
+    const int64_t k_blocks = (k + 63) / 64;
+    *full_tiles = static_cast<uint32_t>(tiles);
+    *split = 0;
+    *bytes = 0;
+    if (workers < 2 || tiles <= workers) return;            // a single partial wave: the split-K kernels' territory
+    const int64_t rem = tiles % workers;
+    if (rem == 0 || rem * 2 > workers) return;
+    int64_t s_max = workers / rem;
+    if (s_max > 8) s_max = 8;
+    if (s_max > k_blocks / 8) s_max = k_blocks / 8;
+    const double tile_us = 0.38 * static_cast<double>(k_blocks);
+    double best = 0.6 * tile_us;
+    int64_t s = 0;
+    for (int64_t c = 2; c <= s_max; ++c) {
+        const double cost = tile_us / c + 3.2 * (c - 1) + 4.0;
+        if (cost < best) { best = cost; s = c; }
+    }
+    if (s < 2) return;
+    *full_tiles = static_cast<uint32_t>(tiles - rem);
+    *split = static_cast<uint32_t>(s);
+    const size_t parts = static_cast<size_t>(rem) * (s - 1) * 2;
+    const size_t flag_bytes = (parts * kEpiWarps * sizeof(uint32_t) + 255) / 256 * 256;
+    *bytes = flag_bytes + parts * kBM * 256 * sizeof(float);
+}
+
+namespace {
+
 template <int CTA_GROUP, int BN, int STAGES, bool BF16>
 cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t stream) {
     using C = Cfg<CTA_GROUP, BN, STAGES>;
@@ -1060,6 +1237,23 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
     uint64_t workers = static_cast<uint64_t>(sms / CTA_GROUP);
     if (tiles < workers) workers = tiles;
 
+    TailArgs tail = {static_cast<uint32_t>(tiles), 0u, nullptr, nullptr};
+    if (CTA_GROUP == 2 && BN == 256 && g.workspace && g.n_extra_dst == 0) {
+        uint32_t full = 0, split = 0;
+        size_t need = 0;
+        plan_tail(g.m, g.n, g.k, static_cast<int>(workers), &full, &split, &need);
+        if (split >= 2 && need <= g.workspace_bytes) {
+            const size_t parts = static_cast<size_t>(tiles - full) * (split - 1) * 2;
+            const size_t flag_bytes = (parts * kEpiWarps * sizeof(uint32_t) + 255) / 256 * 256;
+            cudaError_t e = cudaMemsetAsync(g.workspace, 0, flag_bytes, stream);
+            if (e != cudaSuccess) return e;
+            tail.full_tiles = full;
+            tail.split = split;
+            tail.flags = static_cast<uint32_t *>(g.workspace);
+            tail.ws = reinterpret_cast<float *>(static_cast<uint8_t *>(g.workspace) + flag_bytes);
+        }
+    }
+
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(workers * CTA_GROUP), 1, 1);
     cfg.blockDim = dim3(kThreads, 1, 1);
@@ -1076,7 +1270,7 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
     const uint32_t flags = env_flags >= 0 ? static_cast<uint32_t>(env_flags) : kDefaultFlags;
     return cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b, tm_c, n_dst, static_cast<uint32_t>(g.m),
                               static_cast<uint32_t>(g.n), static_cast<uint32_t>(g.k), group_m, flags,
-                              make_epi(g), d.status_word);
+                              make_epi(g), tail, d.status_word);
 }
 
 template <int BN, int STAGES, bool BF16>
@@ -1289,6 +1483,20 @@ int hgemm_launch(const GemmArgs &g, int variant, int block_n, int max_sms, cudaS
     }
     if (e != cudaSuccess) { *cuda_err = e; return kLaunchCuda; }
     return kLaunchOk;
+}
+
+// Bytes of workspace with which hgemm_launch (automatic configuration, all SMs) would split the last wave of this
+// shape; 0 when it would not.
+size_t hgemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int sm_count) {
+    if (m <= 256 || k <= 0 || n <= 0) return 0;      // small m: skinny / split-K / one-CTA kernels
+    GemmArgs g{nullptr, nullptr, nullptr, m, n, k, k, k, n, true};
+    int variant = 0, block_n = 0;
+    choose_config(g, sm_count, &variant, &block_n);
+    if (variant != 2 || block_n != 256) return 0;
+    uint32_t full = 0, split = 0;
+    size_t bytes = 0;
+    plan_tail(m, n, k, sm_count / 2, &full, &split, &bytes);
+    return split >= 2 ? bytes : 0;
 }
 
 int gemm_device_status(int *out, cudaStream_t stream, cudaError_t *cuda_err) {

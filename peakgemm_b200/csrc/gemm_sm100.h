@@ -22,6 +22,8 @@ struct GemmArgs {
     int64_t ldr = 0;
     bool pdl_wait = false;              // the epilogue waits for the preceding kernel of the stream before it reads
                                         // row_scale (programmatic dependent launch); the main loop does not wait
+    void *workspace = nullptr;          // optional scratch for the tail split of the 256-wide CTA-pair kernel
+    size_t workspace_bytes = 0;
 };
 
 enum LaunchResult { kLaunchOk = 0, kLaunchCuda = 1, kLaunchNotSm100 = 2, kLaunchBadConfig = 3 };
@@ -33,6 +35,9 @@ int hgemm_launch(const GemmArgs &g, int variant, int block_n, int max_sms, cudaS
 
 // Resolves variant/block_n == 0 to concrete values for a device with sm_count SMs.
 void choose_config(const GemmArgs &g, int sm_count, int *variant, int *block_n);
+
+// Workspace (bytes) that lets hgemm_launch split the last, partial wave of this shape over idle SM pairs; 0 if none.
+size_t hgemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int sm_count);
 
 // Synchronises the stream, returns and clears the kernels' device status word.
 int gemm_device_status(int *out, cudaStream_t stream, cudaError_t *cuda_err);

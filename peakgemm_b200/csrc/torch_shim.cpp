@@ -63,6 +63,16 @@ void gemm_peak(Tensor &c, Tensor &a, Tensor &b, int64_t m, int64_t n, int64_t k)
         return;
     }
     const int dt = dtype_code(a, "gemm_peak");
+    // Shapes whose last wave of tiles is mostly empty run that wave split over k; the scratch for the partial
+    // sums comes from torch's caching allocator (stream-ordered, no cudaMalloc in steady state, capturable).
+    const size_t ws_bytes = pg_hgemm_workspace_bytes(m, n, k);
+    if (ws_bytes > 0) {
+        Tensor ws = at::empty({static_cast<int64_t>(ws_bytes)}, a.options().dtype(at::kByte));
+        check_status(pg_hgemm_ws(c.data_ptr(), a.data_ptr(), b.data_ptr(), m, n, k, k, k, n, dt, ws.data_ptr(),
+                                 ws_bytes, stream.stream()),
+                     "gemm_peak");
+        return;
+    }
     check_status(pg_hgemm(c.data_ptr(), a.data_ptr(), b.data_ptr(), m, n, k, k, k, n, dt, stream.stream()),
                  "gemm_peak");
 }

@@ -20,7 +20,7 @@ def declared_functions():
 
 def test_header_declares_the_expected_surface():
     names = declared_functions()
-    for must in ("pg_hgemm", "pg_hgemm_ex", "pg_hgemm_fused", "pg_rmsnorm_rstd", "pg_hgemm_multi", "pg_sgemm", "pg_hgemm_config", "pg_rmsnorm_fwd", "pg_rmsnorm_bwd",
+    for must in ("pg_hgemm", "pg_hgemm_ex", "pg_hgemm_ws", "pg_hgemm_workspace_bytes", "pg_hgemm_fused", "pg_rmsnorm_rstd", "pg_hgemm_multi", "pg_sgemm", "pg_hgemm_config", "pg_rmsnorm_fwd", "pg_rmsnorm_bwd",
                  "pg_rmsnorm_bwd_workspace_bytes", "pg_rmsnorm_bwd_static", "pg_device_status",
                  "pg_status_string", "pg_last_cuda_error", "pg_version", "pg_peer_alloc", "pg_peer_open",
                  "pg_peer_close", "pg_peer_free", "pg_probe_tensor_peak", "pg_probe_copy"):
@@ -79,6 +79,10 @@ def test_argument_checks_return_before_any_cuda_call():
     assert L.pg_rmsnorm_bwd_static(p, p, p, p, p, 4, 60, 1e-6, 1, None) == 3
     assert L.pg_rmsnorm_bwd_static(p, p, p, p, p, 4, 64, 1e-6, 9, None) == 1
     assert L.pg_device_status(None, None) == 1
+    assert L.pg_hgemm_ws(p, p, p, 0, 64, 64, 64, 64, 64, 1, None, 0, None) == 0              # m == 0: no-op
+    assert L.pg_hgemm_ws(p, p, p, 64, 64, 64, 64, 64, 64, 1, p + 16, 1 << 20, None) == 2     # workspace alignment
+    assert L.pg_hgemm_ws(p, p, p, 64, 12, 64, 64, 64, 12, 1, None, 0, None) == 3             # n % 8
+    assert L.pg_hgemm_workspace_bytes(0, 64, 64) == 0
     fu = lambda *a: L.pg_hgemm_fused(*a)         # noqa: E731
     assert fu(p, p, p, 0, 64, 64, 64, 64, 64, p, p, p, 64, 1, 0, None) == 0        # m == 0: no-op
     assert fu(p, p, p, 64, 64, 0, 0, 0, 64, None, None, None, 0, 1, 0, None) == 3  # k == 0 not accepted here

@@ -329,3 +329,61 @@ def test_roofline_probes(cuda):
     torch.cuda.synchronize()
     assert torch.equal(dst, src)
     assert capi.lib().pg_probe_tensor_peak(5, 10, None, None) == 1
+
+
+# ---- tail split (pg_hgemm_ws): the last, partial wave of tiles cut into k-slices over the idle SM pairs
+@pytest.mark.parametrize("dtype", [BF16, F16])
+@pytest.mark.parametrize("m,n,k", [
+    (4096, 4096, 14336),    # 256 tiles on 74 pairs: remainder 34 -> 2 slices
+    (1024, 14336, 8192),    # remainder 2 -> 4 slices
+    (1024, 14336, 16384),   # remainder 2 -> 6 slices
+    (1000, 14328, 8256),    # tails in m, n and k
+])
+def test_tail_split_matches_oracle_and_plain_kernel(cuda, m, n, k, dtype):
+    from peakgemm_b200 import capi
+
+    need = capi.hgemm_workspace_bytes(m, n, k)
+    assert need > 0, "this shape is expected to qualify for the tail split on a 148-SM device"
+    a, b = oracle.gemm_inputs_uniform(m, n, k, dtype, 15)
+    ad, bd = a.cuda(), b.cuda()
+    ws = torch.full((need,), 0xAB, dtype=torch.uint8, device="cuda")       # dirty on purpose
+    split = helpers.garbage_like((m, n), dtype, "cuda")
+    again = helpers.garbage_like((m, n), dtype, "cuda")
+    plain = helpers.garbage_like((m, n), dtype, "cuda")
+    small = helpers.garbage_like((m, n), dtype, "cuda")
+    capi.hgemm_ws(split, ad, bd, ws)
+    capi.hgemm_ws(again, ad, bd, ws)                 # same stream: the second call reuses the buffer after the first
+    capi.hgemm(plain, ad, bd)
+    capi.hgemm_ws(small, ad, bd, ws[:need // 2])     # too small: no split, same kernel as the plain call
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0
+    helpers.check_gemm(split, a, b, exact_rows=False)
+    assert torch.equal(split.view(torch.int16), again.view(torch.int16)), "tail split is not deterministic"
+    assert torch.equal(small.view(torch.int16), plain.view(torch.int16))
+    # only the remainder tiles may differ from the plain kernel, and only by fp32 summation order
+    diff = (split.float() - plain.float()).abs()
+    assert diff.max().item() <= 2.0 ** -6 * plain.float().abs().max().item()
+    changed = (diff > 0).float().mean().item()
+    assert changed < 0.2, changed
+
+
+def test_tail_split_not_offered_where_it_cannot_help(cuda):
+    from peakgemm_b200 import capi
+
+    assert capi.hgemm_workspace_bytes(8192, 8192, 8192) == 0      # remainder 62 of 74: more than half a wave
+    assert capi.hgemm_workspace_bytes(2048, 2048, 2048) == 0      # a single partial wave
+    assert capi.hgemm_workspace_bytes(128, 4096, 4096) == 0       # small m: other kernels
+    assert capi.hgemm_workspace_bytes(4096, 4096, 256) == 0       # k too short to slice
+    assert capi.hgemm_workspace_bytes(1024, 14336, 4096) == 0     # 24 us tiles: reading the partial sums would cost the gain
+
+
+def test_operator_uses_the_tail_split(cuda):
+    import PeakGemm
+
+    m, n, k = 1024, 14336, 8192
+    assert torch.ops.PeakGemm.gemm_peak is not None
+    a, b = oracle.gemm_inputs_llm(m, n, k, BF16, 16)
+    c = helpers.garbage_like((m, n), BF16, "cuda")
+    PeakGemm.gemm_peak(c, a.cuda(), b.cuda())
+    torch.cuda.synchronize()
+    helpers.check_gemm(c, a, b, exact_rows=False)
