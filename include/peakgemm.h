@@ -112,7 +112,9 @@ int pg_hgemm_ex(void *c, const void *a, const void *b,
  * current device (0: this shape would not be split; then workspace may be NULL).  A smaller or NULL
  * workspace simply disables the split.  workspace: 256-byte aligned device memory, private to this call until
  * the kernel has finished (two calls that overlap on the GPU need two buffers); it needs no
- * initialisation (the call clears the flag words it uses with one cudaMemsetAsync on `stream`).
+ * initialisation (the call clears the flag words it uses with one cudaMemsetAsync on `stream`).  A split
+ * launch is a cooperative launch (the tile owners wait, bounded, for helper CTAs of the same grid); where
+ * the device refuses that, the call runs unsplit.
  * The reference has no counterpart: it launches one CTA per tile (get_grid, hgemm_wmma_impl.h:373-378).
  */
 size_t pg_hgemm_workspace_bytes(int64_t m, int64_t n, int64_t k);

@@ -1259,7 +1259,7 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = C::kSmemBytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
+    cudaLaunchAttribute attr[3];
     cfg.attrs = attr;
     cfg.numAttrs = fill_attrs(attr, CTA_GROUP, g);
     // Benchmark overrides, read once: PEAKGEMM_TUNE_GROUP_M (raster band height in tiles),
@@ -1268,6 +1268,20 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
     static const int env_flags = getenv("PEAKGEMM_TUNE_FLAGS") ? atoi(getenv("PEAKGEMM_TUNE_FLAGS")) : -1;
     const uint32_t group_m = env_group_m > 0 ? static_cast<uint32_t>(env_group_m) : 16 / CTA_GROUP;
     const uint32_t flags = env_flags >= 0 ? static_cast<uint32_t>(env_flags) : kDefaultFlags;
+    if (tail.split >= 2) {
+        // Owners wait for helper CTAs of the same grid: ask for a cooperative launch, which starts the grid only
+        // when all of it can be resident at once.  If the device refuses, run without the split.
+        attr[cfg.numAttrs].id = cudaLaunchAttributeCooperative;
+        attr[cfg.numAttrs].val.cooperative = 1;
+        ++cfg.numAttrs;
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b, tm_c, n_dst, static_cast<uint32_t>(g.m),
+                                                 static_cast<uint32_t>(g.n), static_cast<uint32_t>(g.k), group_m,
+                                                 flags, make_epi(g), tail, d.status_word);
+        if (e == cudaSuccess) return e;
+        cudaGetLastError();
+        --cfg.numAttrs;
+        tail = TailArgs{static_cast<uint32_t>(tiles), 0u, nullptr, nullptr};
+    }
     return cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b, tm_c, n_dst, static_cast<uint32_t>(g.m),
                               static_cast<uint32_t>(g.n), static_cast<uint32_t>(g.k), group_m, flags,
                               make_epi(g), tail, d.status_word);

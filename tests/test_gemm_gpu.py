@@ -364,7 +364,7 @@ def test_tail_split_matches_oracle_and_plain_kernel(cuda, m, n, k, dtype):
     diff = (split.float() - plain.float()).abs()
     assert diff.max().item() <= 2.0 ** -6 * plain.float().abs().max().item()
     changed = (diff > 0).float().mean().item()
-    assert changed < 0.2, changed
+    assert 0.0 < changed < 0.2, changed        # > 0: the split really ran (its tiles sum in another order)
 
 
 def test_tail_split_not_offered_where_it_cannot_help(cuda):
