@@ -36,7 +36,7 @@ if REPO not in sys.path:
     sys.path.insert(0, REPO)
 
 M = N = K = 8192
-WORKLOAD = "bf16 GEMM m=n=k=8192 TN (A[m,k] row-major, B[n,k]), U[-1,1] seed 1 (BASELINE configs[1])"
+WORKLOAD = "bf16 GEMM m=n=k=8192 TN (A[m,k] row-major, B[n,k]), U[-1,1] seed 1 (benchmark configs[1])"
 METRIC = "hgemm_bf16_tflops_8192"
 UNIT = "TFLOP/s"
 
@@ -249,7 +249,7 @@ def probes() -> dict:
 
 
 def shape_sweep(peaks: dict) -> list:
-    """BASELINE configs 2 and 3: every shape, ours (automatic configuration) against cuBLAS on the same GPU.
+    """benchmark configs 2 and 3: every shape, ours (automatic configuration) against cuBLAS on the same GPU.
 
     Throughput timing as the reference's Python benchmark does it (test/test_gemm.py:62-96): several
     independent (B, C) sets are rotated through back-to-back launches, enough of them (>= 256 MB of B) that a
@@ -303,7 +303,7 @@ def shape_sweep(peaks: dict) -> list:
 
 
 def chain_sweep() -> list:
-    """RMSNorm -> projection at the LLM shapes of BASELINE config 3 (k = 4096 hidden size), four ways on one GPU:
+    """RMSNorm -> projection at the LLM shapes of benchmark config 3 (k = 4096 hidden size), four ways on one GPU:
       two_op      rms_norm_fwd then gemm_peak (y written and re-read)
       fused       rms_norm_rstd then gemm_peak_fused over the raw x (rstd applied in the epilogue)
       fused_pdl   the same with the GEMM launched under programmatic stream serialisation (main loop overlaps
@@ -384,7 +384,7 @@ def chain_sweep() -> list:
 
 
 def config5(args) -> None:
-    """BASELINE config 5: m = n = 32768, k = 16384 bf16, B column-sharded over the ranks (strong scaling),
+    """benchmark config 5: m = n = 32768, k = 16384 bf16, B column-sharded over the ranks (strong scaling),
     timed without a gather, with the all-gather (native shard-major result) and with the copy to row-major."""
     import torch
     import torch.distributed as dist
@@ -458,11 +458,11 @@ def main() -> None:
     ap.add_argument("--size", type=int, default=8192,
                     help="m=n=k of the GEMM; anything but 8192 is a profiling case, not the headline workload")
     ap.add_argument("--config5", action="store_true",
-                    help="BASELINE config 5 (32768 x 32768 x 16384 sharded over the ranks, with and without the "
+                    help="benchmark config 5 (32768 x 32768 x 16384 sharded over the ranks, with and without the "
                          "all-gather); prints one JSON object and exits")
     ap.add_argument("--probe", action="store_true", help="run only the roofline probes; prints one JSON object and exits")
     ap.add_argument("--sweep", action="store_true",
-                    help="BASELINE configs 2 and 3 (every shape) against cuBLAS; prints one JSON object and exits")
+                    help="benchmark configs 2 and 3 (every shape) against cuBLAS; prints one JSON object and exits")
     ap.add_argument("--chain", action="store_true",
                     help="RMSNorm -> projection chains (two operators, fused, fused + overlapped launch, torch); "
                          "prints one JSON object and exits")

@@ -63,7 +63,7 @@ def test_pair_variants(cuda, block_n, dtype):
     (64, 128, 2048, 64),      # 2 tiles  -> S=8, 8 columns per CTA
     (64, 128, 2048, 128),     # 1 tile   -> S=8, 16 columns per CTA
     (128, 1024, 1024, 128),   # 8 tiles  -> S=8
-    (16, 4096, 4096, 0),      # BASELINE config 3 shape: 32 tiles of 128 -> S=4
+    (16, 4096, 4096, 0),      # benchmark config 3 shape: 32 tiles of 128 -> S=4
     (128, 4096, 1024, 64),    # 64 tiles -> S=2
     (100, 520, 1000, 0),      # tails in m, n and k
     (64, 2048, 576, 128),     # 9 k-blocks over S=4: the last CTA's slice is empty
@@ -98,7 +98,7 @@ def test_split_k_is_deterministic_and_refuses_unsplittable_shapes(cuda):
 @pytest.mark.parametrize("m,n,k", [
     (16, 2048, 2048),      # S=8, 16 rows per CTA
     (1, 2048, 4096),       # a single token
-    (16, 4096, 4096),      # S=4 (BASELINE config 3)
+    (16, 4096, 4096),      # S=4 (benchmark config 3)
     (17, 4096, 1024),      # 32-token tile, S=4
     (33, 8192, 512),       # 64-token tile, S=2
     (64, 8192, 4096),      # full 64-token tile
@@ -233,7 +233,7 @@ def test_argument_errors(cuda):
     assert L.pg_hgemm_ex(p, p, p, 128, 64, 64, 64, 64, 64, 1, 1, 96, 0, None) == 1  # block_n
 
 
-# ---- BASELINE configurations
+# ---- the benchmark configurations
 def test_config1_bf16_2048(cuda):
     """bf16 m=n=k=2048, U[-1,1], seed 0, automatic configuration, exact oracle too."""
     err, tol = run_case(2048, 2048, 2048, BF16, 0, 0, seed=0, exact=True)

@@ -91,7 +91,7 @@ def test_gemm_exact_edge_shapes():
 
 
 def test_config1_exact_vs_fp32_matmul():
-    """BASELINE config 1 on the CPU: the two forms of the oracle agree far inside the acceptance bound."""
+    """benchmark config 1 on the CPU: the two forms of the oracle agree far inside the acceptance bound."""
     a, b = oracle.gemm_inputs_uniform(2048, 2048, 2048, torch.bfloat16, 0)
     exact = oracle.gemm_exact_acc(a, b)
     fast = oracle.gemm_fp32(a, b)

@@ -69,7 +69,7 @@ def test_bwd_shapes(cuda, rows, h, dtype):
 
 @pytest.mark.parametrize("h", [4096, 8192])
 def test_config4_full_size(cuda, h):
-    """BASELINE config 4: x [32768, h] bf16, seed 3, eps 1e-6."""
+    """benchmark config 4: x [32768, h] bf16, seed 3, eps 1e-6."""
     run_fwd(32768, h, BF16)
     run_bwd(32768, h, BF16)
 
