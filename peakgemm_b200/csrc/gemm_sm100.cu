@@ -694,14 +694,16 @@ hgemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     if (warp == 0) {
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
+            // the weights pass through once (evict first); the activations are what every CTA re-reads (evict last)
+            const uint64_t pol_stream = l2_policy_evict_first(), pol_keep = l2_policy_evict_last();
             for (uint32_t kb = kb0; kb < kb1; ++kb) {
                 if (!wait_bar(bar_empty + stage * 8, phase ^ 1u, ctx, kStProducerEmpty)) break;
                 mbar_arrive_expect_tx(bar_full + stage * 8, C::kStageBytes);
                 const int32_t kx = static_cast<int32_t>(kb * kBK);
-                tma_load_2d(smem_base + C::kOffA + stage * C::kABytes, &tm_a, bar_full + stage * 8, kx,
-                            static_cast<int32_t>(mi * kBM));
-                tma_load_2d(smem_base + C::kOffB + stage * C::kBBytes, &tm_b, bar_full + stage * 8, kx,
-                            static_cast<int32_t>(ni * BN));
+                tma_load_2d_hint(smem_base + C::kOffA + stage * C::kABytes, &tm_a, bar_full + stage * 8, kx,
+                                 static_cast<int32_t>(mi * kBM), pol_keep);
+                tma_load_2d_hint(smem_base + C::kOffB + stage * C::kBBytes, &tm_b, bar_full + stage * 8, kx,
+                                 static_cast<int32_t>(ni * BN), pol_stream);
                 if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             }
         }
@@ -903,13 +905,16 @@ hgemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_con
     if (warp == 0) {
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
+            // the weights pass through once (evict first); the activations are what every CTA re-reads (evict last)
+            const uint64_t pol_stream = l2_policy_evict_first(), pol_keep = l2_policy_evict_last();
             for (uint32_t kb = kb0; kb < kb1; ++kb) {
                 if (!wait_bar(bar_empty + stage * 8, phase ^ 1u, ctx, kStProducerEmpty)) break;
                 mbar_arrive_expect_tx(bar_full + stage * 8, C::kStageBytes);
                 const int32_t kx = static_cast<int32_t>(kb * kBK);
-                tma_load_2d(smem_base + C::kOffW + stage * C::kWBytes, &tm_w, bar_full + stage * 8, kx,
-                            static_cast<int32_t>(ni * kBM));
-                tma_load_2d(smem_base + C::kOffT + stage * C::kTBytes, &tm_tok, bar_full + stage * 8, kx, 0);
+                tma_load_2d_hint(smem_base + C::kOffW + stage * C::kWBytes, &tm_w, bar_full + stage * 8, kx,
+                                 static_cast<int32_t>(ni * kBM), pol_stream);
+                tma_load_2d_hint(smem_base + C::kOffT + stage * C::kTBytes, &tm_tok, bar_full + stage * 8, kx, 0,
+                                 pol_keep);
                 if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             }
         }
@@ -1267,7 +1272,9 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
     static const int env_group_m = getenv("PEAKGEMM_TUNE_GROUP_M") ? atoi(getenv("PEAKGEMM_TUNE_GROUP_M")) : 0;
     static const int env_flags = getenv("PEAKGEMM_TUNE_FLAGS") ? atoi(getenv("PEAKGEMM_TUNE_FLAGS")) : -1;
     const uint32_t group_m = env_group_m > 0 ? static_cast<uint32_t>(env_group_m) : 16 / CTA_GROUP;
-    const uint32_t flags = env_flags >= 0 ? static_cast<uint32_t>(env_flags) : kDefaultFlags;
+    // one tile row (m <= 128): every weight byte is read exactly once, so B streams through L2 (evict first)
+    const uint32_t shape_flags = (CTA_GROUP == 1 && g.m <= 128) ? kFlagBEvictFirst : 0u;
+    const uint32_t flags = env_flags >= 0 ? static_cast<uint32_t>(env_flags) : (kDefaultFlags | shape_flags);
     if (tail.split >= 2) {
         // Owners wait for helper CTAs of the same grid: ask for a cooperative launch, which starts the grid only
         // when all of it can be resident at once.  If the device refuses, run without the split.
