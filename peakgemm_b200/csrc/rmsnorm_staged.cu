@@ -76,9 +76,11 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, const Wa
 }
 
 // 1-D bulk copy global -> shared; both addresses 16-byte aligned, bytes % 16 == 0.
-__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void *src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void *src, uint32_t bytes, uint32_t bar,
+                                          uint64_t policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+                 "[%0], [%1], %2, [%3], %4;"
+                 ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar), "l"(policy)
                  : "memory");
 }
 
@@ -202,13 +204,14 @@ rms_staged_kernel(uint4 *__restrict__ out, float *__restrict__ partial, const ui
         if (lane == 0) {
             int slot = 0;
             uint32_t phase = 0;
+            const uint64_t pol = l2_policy_evict_first();     // every row is read exactly once
             for (int64_t i = 0; i < my_rows; ++i) {
                 if (!wait_bar(bar_empty + slot * 8, phase ^ 1u, ctx, kStRmsProducer)) break;
                 const int64_t row = blockIdx.x + i * gridDim.x;
                 mbar_arrive_expect_tx(bar_full + slot * 8, L.slot_bytes);
                 const uint32_t dst = sbase + L.off_slot + slot * L.slot_bytes;
-                bulk_load(dst, x + row * h8, L.row_bytes, bar_full + slot * 8);
-                if constexpr (BWD) bulk_load(dst + L.row_bytes, dy + row * h8, L.row_bytes, bar_full + slot * 8);
+                bulk_load(dst, x + row * h8, L.row_bytes, bar_full + slot * 8, pol);
+                if constexpr (BWD) bulk_load(dst + L.row_bytes, dy + row * h8, L.row_bytes, bar_full + slot * 8, pol);
                 if (++slot == stages) { slot = 0; phase ^= 1u; }
             }
         }
