@@ -36,14 +36,18 @@ using namespace ptx;
 namespace {
 
 // Consumer threads per CTA (G groups x T threads); the producer warp comes on top.  Forward: up to 960 (more rows
-// in flight per SM: its per-row chain is latency-bound and needs few registers); backward: 512 (its dgamma
-// shares and both operands need ~96 registers per thread).
-template <bool BWD>
+// in flight per SM: its per-row chain is latency-bound and needs few registers) — 768 when a thread owns 4 or more
+// column vectors, which is all that shape uses (3 groups of 256) and leaves 80 registers per thread, enough to keep
+// its gamma values in registers; backward: 512 (its dgamma shares and both operands need ~96 registers per thread).
+template <bool BWD, int VPT>
 struct Threads {
-    static constexpr int kConsumers = BWD ? 512 : 960;     // + 32 <= 1024 threads per CTA
+    static constexpr int kConsumers = BWD ? 512 : (VPT >= 4 ? 768 : 960);     // + 32 <= 1024 threads per CTA
     static constexpr int kTotal = kConsumers + 32;
 };
+template <bool BWD> struct RowIndex { using type = int64_t; };
+template <> struct RowIndex<true> { using type = int; };
 constexpr int kMaxStages = 16;
+constexpr int kGammaRegsMaxVpt = 4;     // forward: gamma in registers up to this many vectors per thread
 constexpr uint64_t kWaitTimeoutNs = 2000000000ull;
 constexpr uint32_t kSmemBudget = 200 * 1024;      // bytes of dynamic shared memory we ask for at most
 
@@ -151,13 +155,13 @@ __host__ __device__ inline Layout make_layout(int h, bool bwd, int stages) {
 // [32768, h] bf16: backward h = 8192 269 -> 250 us with INCR, but forward h = 4096 91 -> 98 us and backward
 // h = 4096 136 -> 139 us), so the host picks per shape.
 template <bool BWD, int VPT, bool BF16, bool INCR>
-__global__ void __launch_bounds__(Threads<BWD>::kTotal, 1)
+__global__ void __launch_bounds__(Threads<BWD, VPT>::kTotal, 1)
 rms_staged_kernel(uint4 *__restrict__ out, float *__restrict__ partial, const uint4 *__restrict__ x,
                   const uint4 *__restrict__ dy, const float *__restrict__ gamma, int64_t rows, int h8,
                   float h_f, float eps, int stages, int T, int G, int *status) {
     extern __shared__ __align__(128) uint8_t smem[];
-    constexpr int kMaxConsumers = Threads<BWD>::kConsumers;
-    constexpr int kThreads = Threads<BWD>::kTotal;
+    constexpr int kMaxConsumers = Threads<BWD, VPT>::kConsumers;
+    constexpr int kThreads = Threads<BWD, VPT>::kTotal;
     const int h = h8 * 8;
     const Layout L = make_layout(h, BWD, stages);
     const uint32_t sbase = smem_u32(smem);
@@ -226,7 +230,27 @@ rms_staged_kernel(uint4 *__restrict__ out, float *__restrict__ partial, const ui
         uint32_t phase = 0;
         uint4 *orow = out + (static_cast<int64_t>(blockIdx.x) + static_cast<int64_t>(g) * gridDim.x) * h8;
         const int64_t orow_step = static_cast<int64_t>(G) * gridDim.x * h8;
-        for (int64_t i = g; i < my_rows; i += G, it ^= 1) {
+        // Forward: a thread scales the same columns in every row, so its gamma values stay in registers
+        // (the backward pass has its dgamma shares there instead and reads gamma from shared memory).
+        constexpr bool kGammaRegs = !BWD && VPT <= kGammaRegsMaxVpt;
+        float gm_reg[kGammaRegs ? VPT : 1][8];
+        if constexpr (kGammaRegs) {
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const int idx = min(t + T * j, h8 - 1);
+                const float4 g0 = reinterpret_cast<const float4 *>(s_gamma)[2 * idx];
+                const float4 g1 = reinterpret_cast<const float4 *>(s_gamma)[2 * idx + 1];
+                gm_reg[j][0] = g0.x; gm_reg[j][1] = g0.y; gm_reg[j][2] = g0.z; gm_reg[j][3] = g0.w;
+                gm_reg[j][4] = g1.x; gm_reg[j][5] = g1.y; gm_reg[j][6] = g1.z; gm_reg[j][7] = g1.w;
+            }
+        }
+        // Row counter: 32-bit in the backward kernel (rows per CTA are far below 2^31; the 64-bit i % stages and
+        // i / stages cost ~100 instructions per row and thread: backward h = 4096 132 -> 128 us), 64-bit in the
+        // forward kernel, which measured SLOWER with the cheaper form (89 -> 93 us at h = 4096, as it did with the
+        // incremental form above): its consumers then return to polling the next slot's barrier sooner.
+        using RowIdx = typename RowIndex<BWD>::type;
+        const RowIdx my_rows_i = static_cast<RowIdx>(my_rows);
+        for (RowIdx i = g; i < my_rows_i; i += G, it ^= 1) {
             if constexpr (INCR) {
                 if (i != g) {
                     slot += G;
@@ -236,7 +260,7 @@ rms_staged_kernel(uint4 *__restrict__ out, float *__restrict__ partial, const ui
             } else {
                 slot = static_cast<int>(i % stages);
                 phase = static_cast<uint32_t>(i / stages) & 1u;
-                orow = out + (static_cast<int64_t>(blockIdx.x) + i * gridDim.x) * h8;
+                orow = out + (static_cast<int64_t>(blockIdx.x) + static_cast<int64_t>(i) * gridDim.x) * h8;
             }
             bool ok = wait_bar(bar_full + slot * 8, phase, ctx, kStRmsConsumer);
             ok = __all_sync(0xffffffffu, ok);
@@ -303,9 +327,16 @@ rms_staged_kernel(uint4 *__restrict__ out, float *__restrict__ partial, const ui
             for (int j = 0; j < VPT; ++j) {
                 const int idx = t + T * j;
                 if (idx < h8) {
-                    const float4 g0 = reinterpret_cast<const float4 *>(s_gamma)[2 * idx];
-                    const float4 g1 = reinterpret_cast<const float4 *>(s_gamma)[2 * idx + 1];
-                    const float gm[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+                    float gm[8];
+                    if constexpr (kGammaRegs) {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) gm[e] = gm_reg[j][e];
+                    } else {
+                        const float4 g0 = reinterpret_cast<const float4 *>(s_gamma)[2 * idx];
+                        const float4 g1 = reinterpret_cast<const float4 *>(s_gamma)[2 * idx + 1];
+                        gm[0] = g0.x; gm[1] = g0.y; gm[2] = g0.z; gm[3] = g0.w;
+                        gm[4] = g1.x; gm[5] = g1.y; gm[6] = g1.z; gm[7] = g1.w;
+                    }
                     float xf[8], o[8];
                     unpack8<BF16>(xv[j], xf);
                     if constexpr (BWD) {
@@ -382,7 +413,7 @@ Plan make_plan(int64_t h, bool bwd) {
     const int need = static_cast<int>((h8 + T - 1) / T);
     p.vpt = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
     p.T = T;
-    p.G = (bwd ? Threads<true>::kConsumers : Threads<false>::kConsumers) / T;
+    p.G = (bwd ? Threads<true, 1>::kConsumers : p.vpt >= 4 ? Threads<false, 4>::kConsumers : Threads<false, 1>::kConsumers) / T;
     if (p.G > 8) p.G = 8;
     for (int s = kMaxStages; s >= 2; --s) {
         const Layout l = make_layout(static_cast<int>(h), bwd, s);
@@ -437,7 +468,7 @@ cudaError_t launch_one(void *out, float *partial, const void *x, const void *dy,
         if (e != cudaSuccess) return e;
         attr_done[dev] = true;
     }
-    kernel<<<grid, Threads<BWD>::kTotal, p.smem, stream>>>(static_cast<uint4 *>(out), partial, static_cast<const uint4 *>(x),
+    kernel<<<grid, Threads<BWD, VPT>::kTotal, p.smem, stream>>>(static_cast<uint4 *>(out), partial, static_cast<const uint4 *>(x),
                                                static_cast<const uint4 *>(dy), gamma, rows,
                                                static_cast<int>(h / 8), static_cast<float>(h), eps, p.stages, p.T,
                                                p.G, status);
