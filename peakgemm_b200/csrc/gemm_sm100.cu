@@ -49,6 +49,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <math.h>
 #include <stdlib.h>
 
 #include "gemm_sm100.h"
@@ -1423,6 +1424,37 @@ void choose_splitk(const GemmArgs &g, int sm_count, int block_n, int *bn_out, in
     }
 }
 
+// One tile row (64 < m <= 128): which of the one-CTA persistent kernel (block_n 64/128/256) and the cluster split-K
+// kernel (block_n 64/128, S = 2/4/8) streams the weights fastest.  Model fitted to B200 measurements (us):
+//   t = max(weight bytes / 6.0 TB/s, bytes one CTA pulls / 100 GB/s) + exchange + 6
+// where a CTA pulls (128 + block_n) * 128 bytes per k-block (the A panel comes from L2 but costs SM ingest all the
+// same) and the split-K exchange costs 1.5 + KiB sent / 10.7.  E.g. 128 x 8192 x 8192: one CTA per 64-wide tile
+// 37 (measured 39), split-K 128 x 2: 31 (32); 128 x 4096 x 14336: split-K 64 x 2: 36 (37), 128 x 4: 32 (31).
+// Returns split = 0 for the persistent kernel (block_n then its tile width).
+void plan_one_tile_row(const GemmArgs &g, int sms, int *block_n, int *split) {
+    const double k_blocks = static_cast<double>((g.k + 63) / 64);
+    const double t_dram = static_cast<double>(g.n) * g.k * 2.0 / 6.0e6;
+    double best = 1e300;
+    *block_n = 128;
+    *split = 0;
+    for (int bn = 256; bn >= 64; bn /= 2) {
+        const int64_t tiles = (g.n + bn - 1) / bn;
+        const double waves = static_cast<double>((tiles + sms - 1) / sms);
+        const double t = fmax(t_dram, waves * k_blocks * (128 + bn) * 128.0 / 1.0e5) + 6.0;
+        if (t < best) { best = t; *block_n = bn; *split = 0; }
+    }
+    for (int bn = 128; bn >= 64; bn /= 2) {
+        const int64_t tiles = (g.n + bn - 1) / bn;
+        for (int sp = 2; sp <= 8; sp *= 2) {
+            if (k_blocks < 2 * sp || bn / sp < 8 || tiles * sp * 10 > static_cast<int64_t>(sms) * 11) continue;
+            const double per = ceil(k_blocks / sp);
+            const double exch = 1.5 + (sp - 1.0) / sp * bn * 128 * 4 / 1024.0 / 10.7;
+            const double t = fmax(t_dram, per * (128 + bn) * 128.0 / 1.0e5) + exch + 6.0;
+            if (t < best) { best = t; *block_n = bn; *split = sp; }
+        }
+    }
+}
+
 int hgemm_launch(const GemmArgs &g, int variant, int block_n, int max_sms, cudaStream_t stream,
                  cudaError_t *cuda_err) {
     DeviceInfo *d = nullptr;
@@ -1470,7 +1502,13 @@ int hgemm_launch(const GemmArgs &g, int variant, int block_n, int max_sms, cudaS
         int sk_bn = 0, sk_s = 0;
         choose_splitk(g, sms, block_n == 256 ? 0 : block_n, &sk_bn, &sk_s);
         bool use = sk_s >= 2;
-        if (use && variant == 0) {
+        if (variant == 0 && g.m <= 128 && block_n == 0 && env_split != 0) {
+            int bn = 0, sp = 0;
+            plan_one_tile_row(g, sms, &bn, &sp);
+            use = sp >= 2;
+            if (use) { sk_bn = bn; sk_s = sp; }
+            else { variant = 1; block_n = bn; }
+        } else if (use && variant == 0) {
             int v1 = 1, b1 = 0;
             choose_config(g, sms, &v1, &b1);
             const int64_t tiles1 = ((g.m + 127) / 128) * ((g.n + b1 - 1) / b1);
