@@ -45,6 +45,14 @@
 // Every wait is bounded: a role that waits longer than kWaitTimeoutNs records a
 // code in a device status word, raises a CTA-wide abort flag and all roles fall
 // through to the common teardown (tensor memory is freed, the kernel returns).
+//
+// Optional extras of the same kernel, all off (null pointers) in a plain GEMM:
+//   * fused epilogue terms  out = row_scale[row] * acc + bias[col] + residual[row, col]  (EpiArgs);
+//   * several destinations for the output tile (DstMaps): the column-sharded caller's gather over NVLink;
+//   * tail split (TailArgs): the last partial wave of tiles cut into k-slices over the idle workers, partial
+//     sums through a caller workspace, launched cooperatively.
+// The file also holds the two kernels for few output tiles (cluster split-K, swapped-operand skinny), which
+// share the fused epilogue terms, and the host side: tensor-map cache, configuration choice, launches.
 
 #include <cuda.h>
 #include <cuda_runtime.h>
