@@ -600,7 +600,12 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
             }
             if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         }
-        if (lane == 0) bulk_wait_group<0>();   // shared memory must outlive the stores that read it
+        // Shared memory must outlive the stores that read it; their global writes are complete when the grid is.
+        // With peer destinations the thread waits for the writes themselves, to stay on the safe side of NVLink.
+        if (lane == 0) {
+            if (n_dst == 1) bulk_wait_group_read<0>();
+            else bulk_wait_group<0>();
+        }
         __syncwarp();
     }
 
