@@ -106,7 +106,8 @@ int pg_hgemm_ex(void *c, const void *a, const void *b,
  * pg_hgemm with an optional scratch buffer that lets the kernel split the LAST, partial wave of output
  * tiles: when the tiles do not fill a whole number of waves of the persistent grid and the remainder
  * occupies at most half of the SM pairs and k is long enough for the exchange to pay (about k >= 8192), each
- * remainder tile is cut into 2-8 slices of k that run on the otherwise idle SM pairs; the slices' fp32 partial sums pass through `workspace` and are added in slice
+ * remainder tile is cut into 2-8 slices of k that run on the otherwise idle SM pairs (a problem of at most half
+ * a wave is all remainder: every tile is split); the slices' fp32 partial sums pass through `workspace` and are added in slice
  * order (deterministic) before the one rounding.  Results differ from pg_hgemm only by the fp32 summation
  * order of those tiles.  pg_hgemm_workspace_bytes(m, n, k) gives the size that enables the split on the
  * current device (0: this shape would not be split; then workspace may be NULL).  A smaller or NULL

@@ -1203,14 +1203,20 @@ void plan_tail(int64_t m, int64_t n, int64_t k, int workers, uint32_t *full_tile
     *full_tiles = static_cast<uint32_t>(tiles);
     *split = 0;
     *bytes = 0;
-    if (workers < 2 || tiles <= workers) return;            // a single partial wave: the split-K kernels' territory
-    const int64_t rem = tiles % workers;
+    if (workers < 2) return;
+    // A problem of at most half a wave is all remainder: every tile is split (mid-size m with a long k, where 32
+    // tiles would leave 42 SM pairs idle for the whole run; 512 x 4096 x 14336: 67 -> 54 us, 512 x 4096 x 8192:
+    // 42 -> 37, but 512 x 4096 x 4096: 25.6 -> 27.5).  Nothing runs un-throttled beside it then, so the bar is 0.7
+    // of a tile time instead of 0.6.
+    const bool all_remainder = tiles * 2 <= workers;
+    if (!all_remainder && tiles <= workers) return;
+    const int64_t rem = all_remainder ? tiles : tiles % workers;
     if (rem == 0 || rem * 2 > workers) return;
     int64_t s_max = workers / rem;
     if (s_max > 8) s_max = 8;
     if (s_max > k_blocks / 8) s_max = k_blocks / 8;
     const double tile_us = 0.38 * static_cast<double>(k_blocks);
-    double best = 0.6 * tile_us;
+    double best = (all_remainder ? 0.7 : 0.6) * tile_us;
     int64_t s = 0;
     for (int64_t c = 2; c <= s_max; ++c) {
         const double cost = tile_us / c + 3.2 * (c - 1) + 4.0;
@@ -1254,7 +1260,6 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
     const uint64_t n_tiles = (g.n + BN - 1) / BN;
     const uint64_t tiles = m_tiles * n_tiles;
     uint64_t workers = static_cast<uint64_t>(sms / CTA_GROUP);
-    if (tiles < workers) workers = tiles;
 
     TailArgs tail = {static_cast<uint32_t>(tiles), 0u, nullptr, nullptr};
     if (CTA_GROUP == 2 && BN == 256 && g.workspace && g.n_extra_dst == 0) {
@@ -1262,6 +1267,7 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
         size_t need = 0;
         plan_tail(g.m, g.n, g.k, static_cast<int>(workers), &full, &split, &need);
         if (split >= 2 && need <= g.workspace_bytes) {
+            if (full == 0) workers = tiles * split;     // all remainder: one worker per k-slice
             const size_t parts = static_cast<size_t>(tiles - full) * (split - 1) * 2;
             const size_t flag_bytes = (parts * kEpiWarps * sizeof(uint32_t) + 255) / 256 * 256;
             cudaError_t e = cudaMemsetAsync(g.workspace, 0, flag_bytes, stream);
@@ -1272,6 +1278,7 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
             tail.ws = reinterpret_cast<float *>(static_cast<uint8_t *>(g.workspace) + flag_bytes);
         }
     }
+    if (tail.split < 2 && tiles < workers) workers = tiles;
 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(workers * CTA_GROUP), 1, 1);
@@ -1538,6 +1545,12 @@ int hgemm_launch(const GemmArgs &g, int variant, int block_n, int max_sms, cudaS
             return kLaunchOk;
         }
     }
+    if (variant == 0 && block_n == 0 && g.workspace && g.m > 256 && g.n_extra_dst == 0) {
+        uint32_t full = 0, split = 0;
+        size_t need = 0;
+        plan_tail(g.m, g.n, g.k, sms / 2, &full, &split, &need);
+        if (split >= 2 && full == 0 && need <= g.workspace_bytes) { variant = 2; block_n = 256; }
+    }
     choose_config(g, sms, &variant, &block_n);
 
     if (variant == 1) {
@@ -1561,14 +1574,15 @@ int hgemm_launch(const GemmArgs &g, int variant, int block_n, int max_sms, cudaS
 // shape; 0 when it would not.
 size_t hgemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int sm_count) {
     if (m <= 256 || k <= 0 || n <= 0) return 0;      // small m: skinny / split-K / one-CTA kernels
-    GemmArgs g{nullptr, nullptr, nullptr, m, n, k, k, k, n, true};
-    int variant = 0, block_n = 0;
-    choose_config(g, sm_count, &variant, &block_n);
-    if (variant != 2 || block_n != 256) return 0;
     uint32_t full = 0, split = 0;
     size_t bytes = 0;
     plan_tail(m, n, k, sm_count / 2, &full, &split, &bytes);
-    return split >= 2 ? bytes : 0;
+    if (split < 2) return 0;
+    if (full == 0) return bytes;                      // all remainder: the launch takes the 256-wide pair kernel for it
+    GemmArgs g{nullptr, nullptr, nullptr, m, n, k, k, k, n, true};
+    int variant = 0, block_n = 0;
+    choose_config(g, sm_count, &variant, &block_n);
+    return (variant == 2 && block_n == 256) ? bytes : 0;
 }
 
 int gemm_device_status(int *out, cudaStream_t stream, cudaError_t *cuda_err) {
