@@ -393,3 +393,37 @@ def test_operator_uses_the_tail_split(cuda):
     PeakGemm.gemm_peak(c, a.cuda(), b.cuda())
     torch.cuda.synchronize()
     helpers.check_gemm(c, a, b, exact_rows=False)
+
+
+def test_tail_split_operator_is_capturable(cuda):
+    """The operator on a shape that takes the tail split (scratch from torch's allocator, one memset, a cooperative
+    launch) inside a CUDA graph: the replay on new inputs equals eager execution bit for bit."""
+    import PeakGemm
+    from peakgemm_b200 import capi
+
+    m, n, k = 1024, 14336, 8192
+    assert capi.hgemm_workspace_bytes(m, n, k) > 0
+    a, b = oracle.gemm_inputs_llm(m, n, k, BF16, 17)
+    ad, bd = a.cuda(), b.cuda()
+    c = helpers.garbage_like((m, n), BF16, "cuda")
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        PeakGemm.gemm_peak(c, ad, bd)                 # per-device set-up outside the capture
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        PeakGemm.gemm_peak(c, ad, bd)
+    a2, _ = oracle.gemm_inputs_llm(m, n, k, BF16, 18)
+    ad.copy_(a2)
+    c.fill_(float("nan"))
+    graph.replay()
+    torch.cuda.synchronize()
+    replayed = c.clone()
+    c.fill_(float("nan"))
+    PeakGemm.gemm_peak(c, ad, bd)
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0
+    assert torch.equal(replayed.view(torch.int16), c.view(torch.int16))
+    helpers.check_gemm(c, a2, b, exact_rows=False)
