@@ -427,3 +427,26 @@ def test_tail_split_operator_is_capturable(cuda):
     assert capi.device_status() == 0
     assert torch.equal(replayed.view(torch.int16), c.view(torch.int16))
     helpers.check_gemm(c, a2, b, exact_rows=False)
+
+
+def test_tail_split_on_two_streams_with_separate_workspaces(cuda):
+    """Two split launches in flight on two streams, each with its own workspace (the documented way): both correct."""
+    from peakgemm_b200 import capi
+
+    m, n, k = 1024, 14336, 8192
+    need = capi.hgemm_workspace_bytes(m, n, k)
+    assert need > 0
+    a, b = oracle.gemm_inputs_uniform(m, n, k, BF16, 19)
+    ad, bd = a.cuda(), b.cuda()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    wss = [torch.empty(need, dtype=torch.uint8, device="cuda") for _ in streams]
+    outs = [helpers.garbage_like((m, n), BF16, "cuda") for _ in streams]
+    torch.cuda.synchronize()
+    for rep in range(3):
+        for s, ws, o in zip(streams, wss, outs):
+            with torch.cuda.stream(s):
+                capi.hgemm_ws(o, ad, bd, ws, stream=s)
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0
+    helpers.check_gemm(outs[0], a, b, exact_rows=False)
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
