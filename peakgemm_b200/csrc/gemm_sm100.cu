@@ -485,7 +485,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
             // k-slices of a remainder tile: where this warp's rows of slice j live in the workspace, and its flag
             constexpr uint32_t kPartFloats = kBM * BN;                  // one CTA's partial tile
             const uint32_t n_parts = (u.is_tail && u.slice == 0) ? tail.split - 1u : 0u;
-            const uint32_t part0 = (u.tail_idx * (tail.split - 1u)) * CTA_GROUP + rank;   // slice 1 of this tile
+            const uint32_t part0 = u.is_tail ? (u.tail_idx * (tail.split - 1u)) * CTA_GROUP + rank : 0u;   // slice 1 of this tile
             if (u.is_tail && u.slice > 0) {
                 // ===== helper: fp32 partial sums to the workspace, then the flag =====
                 const uint32_t part = part0 + (u.slice - 1u) * CTA_GROUP;
