@@ -457,6 +457,11 @@ def main() -> None:
     ap.add_argument("--no-extras", action="store_true", help="skip comparators, RMSNorm, e2e and CPU legs")
     ap.add_argument("--size", type=int, default=8192,
                     help="m=n=k of the GEMM; anything but 8192 is a profiling case, not the headline workload")
+    ap.add_argument("--shape", type=int, nargs=3, default=None, metavar=("M", "N", "K"),
+                    help="profiling case: a non-square GEMM instead of the headline workload")
+    ap.add_argument("--cublas", action="store_true",
+                    help="with --no-extras: also run the cuBLAS comparator (torch.matmul) for the same steps after "
+                         "the timed region, so that a profiler sees both kernels in one process")
     ap.add_argument("--config5", action="store_true",
                     help="benchmark config 5 (32768 x 32768 x 16384 sharded over the ranks, with and without the "
                          "all-gather); prints one JSON object and exits")
@@ -474,6 +479,9 @@ def main() -> None:
     if args.size != 8192:
         M = N = K = args.size
         WORKLOAD = f"PROFILING CASE bf16 GEMM m=n=k={args.size} TN (not the headline workload)"
+    if args.shape:
+        M, N, K = args.shape
+        WORKLOAD = f"PROFILING CASE bf16 GEMM m={M} n={N} k={K} TN (not the headline workload)"
 
     if args.impl == "reference":
         run_reference_arm(args)
@@ -644,6 +652,9 @@ def main() -> None:
         line["cpu_baseline"] = cpu_gemm_baseline()
     elif rank == 0 and world > 1:
         line["e2e"] = None
+    if args.no_extras and args.cublas and world == 1:
+        t_cublas = time_cuda(lambda: torch.matmul(a, b.t(), out=c), args.steps, args.warmup)
+        line["cublas"] = {"tflops": flops_step / (t_cublas * 1e-3) / 1e12, "ms": t_cublas}
     line["clocks"] = clocks.summary()
 
     if rank == 0:

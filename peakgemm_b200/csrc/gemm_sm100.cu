@@ -10,6 +10,12 @@
 //                 both CTAs' tensor memory                 (tcgen05 cta_group::2)
 //   BN         tile width (64, 128, 256)
 //   STAGES     depth of the TMA -> MMA shared-memory ring (>= 4)
+//   MT         row blocks per CTA.  1: the tile is 128*CTA_GROUP rows.  2 (CTA pair, BN = 256): the pair owns a
+//              512 x 256 tile as two 256-row blocks that share every k-block of B; their two accumulators fill
+//              tensor memory.  Per flop this moves 25 % fewer operand bytes from L2 into shared memory than the
+//              256 x 256 tile ((512 + 256) against 2 * (256 + 256) rows per two 256 x 256 x 64 blocks of work),
+//              which on a power-capped part is clock: the price is that the epilogue of a tile no longer overlaps
+//              the next tile's first MMAs (the second block's accumulator drains while the first block's restart).
 //
 // Warp roles (192 threads):
 //   warp 0    producer: one thread issues the TMA loads of A and B k-blocks
@@ -100,13 +106,17 @@ enum : int {
     kStEpiTailFlag = 5,
 };
 
-template <int CTA_GROUP, int BN, int STAGES>
+template <int CTA_GROUP, int BN, int STAGES, int MT = 1>
 struct Cfg {
     static constexpr uint32_t kBRows = BN / CTA_GROUP;          // rows of B this CTA loads
-    static constexpr uint32_t kABytes = kBM * kBK * 2;          // 16 KiB
+    static constexpr uint32_t kABox = kBM * kBK * 2;            // one 128-row box of A: 16 KiB
+    static constexpr uint32_t kABytes = MT * kABox;             // MT row blocks of A per stage
     static constexpr uint32_t kBBytes = kBRows * kBK * 2;
     static constexpr uint32_t kStageBytes = kABytes + kBBytes;
-    static constexpr uint32_t kTmemCols = 2 * BN;               // two accumulators
+    // MT == 1: two accumulators, tile i's epilogue overlaps tile i+1's main loop.
+    // MT == 2: the two row blocks' accumulators fill tensor memory; both belong to the tile in flight.
+    static constexpr uint32_t kTmemCols = 2 * BN;
+    static_assert(MT == 1 || (MT == 2 && CTA_GROUP == 2 && BN == 256), "two row blocks: CTA pair, 256 columns");
     static constexpr uint32_t kOffA = 0;
     static constexpr uint32_t kOffB = kOffA + STAGES * kABytes;
     static constexpr uint32_t kOffC = kOffB + STAGES * kBBytes;
@@ -295,15 +305,16 @@ __device__ __forceinline__ bool wait_flag(const uint32_t *flag, const WaitCtx &c
     return true;
 }
 
-template <int CTA_GROUP, int BN, int STAGES, bool BF16>
+template <int CTA_GROUP, int BN, int STAGES, int MT, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                      const __grid_constant__ CUtensorMap tm_b,
                      const __grid_constant__ DstMaps tm_c, uint32_t n_dst,
                      uint32_t M, uint32_t N, uint32_t K, uint32_t group_m, uint32_t flags, const EpiArgs epi,
                      const TailArgs tail, int *status) {
-    using C = Cfg<CTA_GROUP, BN, STAGES>;
-    constexpr uint32_t kTileM = kBM * CTA_GROUP;
+    using C = Cfg<CTA_GROUP, BN, STAGES, MT>;
+    constexpr uint32_t kBlockM = kBM * CTA_GROUP;         // rows one MMA covers
+    constexpr uint32_t kTileM = kBlockM * MT;
 
     extern __shared__ uint8_t smem_raw[];
     // Swizzled TMA tiles and UMMA descriptors want 1024-byte aligned bases.
@@ -378,7 +389,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                 if (!u.valid) break;
                 uint32_t mi, ni;
                 tile_coords(group_m, u.tile, m_tiles, n_tiles, mi, ni, (flags & kFlagSerpentine) != 0);
-                const int32_t row_a = static_cast<int32_t>(mi * kTileM + rank * kBM);
+                const int32_t row_a = static_cast<int32_t>(mi * kTileM + rank * kBM);    // + mt * kBlockM
                 const int32_t row_b = static_cast<int32_t>(ni * BN + rank * C::kBRows);
                 for (uint32_t kb = u.kb0; kb < u.kb1; ++kb) {
                     if (leader) {
@@ -399,12 +410,17 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                     const uint32_t dst_b = smem_base + C::kOffB + stage * C::kBBytes;
                     const int32_t kx = static_cast<int32_t>(kb * kBK);
                     const uint32_t fb = (CTA_GROUP == 2) ? full0 + stage * 8 : bar_full + stage * 8;
-                    if (hint_a) {
-                        if constexpr (CTA_GROUP == 2) tma_load_2d_pair_hint(dst_a, &tm_a, fb, kx, row_a, pol_a);
-                        else tma_load_2d_hint(dst_a, &tm_a, fb, kx, row_a, pol_a);
-                    } else {
-                        if constexpr (CTA_GROUP == 2) tma_load_2d_pair(dst_a, &tm_a, fb, kx, row_a);
-                        else tma_load_2d(dst_a, &tm_a, fb, kx, row_a);
+#pragma unroll
+                    for (uint32_t mt = 0; mt < MT; ++mt) {
+                        const uint32_t da = dst_a + mt * C::kABox;
+                        const int32_t ra = row_a + static_cast<int32_t>(mt * kBlockM);
+                        if (hint_a) {
+                            if constexpr (CTA_GROUP == 2) tma_load_2d_pair_hint(da, &tm_a, fb, kx, ra, pol_a);
+                            else tma_load_2d_hint(da, &tm_a, fb, kx, ra, pol_a);
+                        } else {
+                            if constexpr (CTA_GROUP == 2) tma_load_2d_pair(da, &tm_a, fb, kx, ra);
+                            else tma_load_2d(da, &tm_a, fb, kx, ra);
+                        }
                     }
                     if (hint_b) {
                         if constexpr (CTA_GROUP == 2) tma_load_2d_pair_hint(dst_b, &tm_b, fb, kx, row_b, pol_b);
@@ -421,34 +437,55 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
     } else if (warp == 1) {
         if (lane == 0 && leader) {
             // ===== MMA issuer =====
-            constexpr uint32_t idesc = instr_desc_f16(BF16, kBM * CTA_GROUP, BN);
+            constexpr uint32_t idesc = instr_desc_f16(BF16, kBlockM, BN);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
             for (uint32_t it = 0; ok; ++it) {
                 const Unit u = unit_at(it, worker, workers, total_tiles, k_blocks, tail);
                 if (!u.valid) break;
-                // the epilogue must have drained this accumulator (passes at once the first two times)
-                ok = wait_bar(bar_acc_empty + acc * 8, acc_phase ^ 1u, ctx, kStMmaAccEmpty);
-                if (!ok) break;
-                tc_fence_after_sync();
-                const uint32_t tmem_d = tmem_base + acc * BN;
+                if constexpr (MT == 1) {
+                    // the epilogue must have drained this accumulator (passes at once the first two times)
+                    ok = wait_bar(bar_acc_empty + acc * 8, acc_phase ^ 1u, ctx, kStMmaAccEmpty);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                }
                 for (uint32_t kb = u.kb0; kb < u.kb1; ++kb) {
                     ok = wait_bar(bar_full + stage * 8, phase, ctx, kStMmaFull);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    const uint64_t da = smem_desc_k_sw128(smem_base + C::kOffA + stage * C::kABytes);
                     const uint64_t db = smem_desc_k_sw128(smem_base + C::kOffB + stage * C::kBBytes);
 #pragma unroll
-                    for (uint32_t k = 0; k < kBK / kUmmaK; ++k) {
-                        // 16 elements of k = 32 bytes inside the 128-byte swizzle row = +2 in the >>4 address field
-                        umma_f16<CTA_GROUP>(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb != u.kb0 || k != 0u) ? 1u : 0u);
+                    for (uint32_t mt = 0; mt < MT; ++mt) {
+                        if constexpr (MT == 2) {
+                            // Row block mt accumulates into accumulator mt.  The previous tile's epilogue drains
+                            // accumulator 0 first: block 0 of this tile restarts while accumulator 1 still drains.
+                            if (kb == u.kb0) {
+                                ok = wait_bar(bar_acc_empty + mt * 8, acc_phase ^ 1u, ctx, kStMmaAccEmpty);
+                                if (!ok) break;
+                                tc_fence_after_sync();
+                            }
+                        }
+                        const uint32_t tmem_d = tmem_base + (MT == 2 ? mt : acc) * BN;
+                        const uint64_t da = smem_desc_k_sw128(smem_base + C::kOffA + stage * C::kABytes + mt * C::kABox);
+#pragma unroll
+                        for (uint32_t k = 0; k < kBK / kUmmaK; ++k) {
+                            // 16 elements of k = 32 bytes inside the 128-byte swizzle row = +2 in the >>4 address field
+                            umma_f16<CTA_GROUP>(tmem_d, da + 2 * k, db + 2 * k, idesc,
+                                                (kb != u.kb0 || k != 0u) ? 1u : 0u);
+                        }
                     }
+                    if (!ok) break;
                     umma_commit<CTA_GROUP>(bar_empty + stage * 8);   // stage free once these MMAs are done
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
-                umma_commit<CTA_GROUP>(bar_acc_full + acc * 8);      // accumulator complete
-                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+                if constexpr (MT == 2) {
+                    umma_commit<CTA_GROUP>(bar_acc_full);            // both accumulators complete
+                    acc_phase ^= 1u;
+                } else {
+                    umma_commit<CTA_GROUP>(bar_acc_full + acc * 8);  // accumulator complete
+                    if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+                }
             }
         }
         __syncwarp();
@@ -470,58 +507,68 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
             tile_coords(group_m, u.tile, m_tiles, n_tiles, mi, ni, (flags & kFlagSerpentine) != 0);
             // All 32 lanes probe: a failed try_wait parks the warp in hardware, so this costs nothing (a
             // one-lane poll with __nanosleep back-off executed 40 % MORE instructions and ran 0.7 % slower).
-            ok = wait_bar(bar_acc_full + acc * 8, acc_phase, ctx, kStEpiAccFull);
+            constexpr uint32_t acc_full_slot = 0;   // MT == 2 signals on slot 0 only
+            const uint32_t full_bar = (MT == 2) ? bar_acc_full + acc_full_slot * 8 : bar_acc_full + acc * 8;
+            ok = wait_bar(full_bar, acc_phase, ctx, kStEpiAccFull);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             if constexpr (CTA_GROUP == 2) {
-                if (leader && e == 0 && lane == 0) mbar_arrive_cluster(peer_acc_full + acc * 8);  // relay
+                if (leader && e == 0 && lane == 0)
+                    mbar_arrive_cluster(peer_acc_full + ((MT == 2) ? 0u : acc) * 8);  // relay
             }
             tc_fence_after_sync();
-            const uint32_t row0 = mi * kTileM + rank * kBM + q * 32u;   // first row of this warp's slab
-            const uint32_t taddr = tmem_base + acc * BN + ((q * 32u) << 16);
             const bool fused = epi.any();
+#pragma unroll 1
+            for (uint32_t mt = 0; mt < MT; ++mt) {
+            const uint32_t a_idx = (MT == 2) ? mt : acc;                // accumulator read here
+            const uint32_t row0 = mi * kTileM + mt * kBlockM + rank * kBM + q * 32u;   // first row of this warp's slab
+            const uint32_t taddr = tmem_base + a_idx * BN + ((q * 32u) << 16);
             const bool row_ok = row0 + lane < M;
             const float rs = fused ? epi_row_scale(epi, row_ok, row0 + lane) : 1.f;
             // k-slices of a remainder tile: where this warp's rows of slice j live in the workspace, and its flag
             constexpr uint32_t kPartFloats = kBM * BN;                  // one CTA's partial tile
-            const uint32_t n_parts = (u.is_tail && u.slice == 0) ? tail.split - 1u : 0u;
-            const uint32_t part0 = u.is_tail ? (u.tail_idx * (tail.split - 1u)) * CTA_GROUP + rank : 0u;   // slice 1 of this tile
-            if (u.is_tail && u.slice > 0) {
-                // ===== helper: fp32 partial sums to the workspace, then the flag =====
-                const uint32_t part = part0 + (u.slice - 1u) * CTA_GROUP;
-                float4 *dst = reinterpret_cast<float4 *>(tail.ws + static_cast<size_t>(part) * kPartFloats) +
-                              (q * 32u + lane);
+            uint32_t n_parts = 0, part0 = 0;
+            bool helper = false;
+            if constexpr (MT == 1) {
+                n_parts = (u.is_tail && u.slice == 0) ? tail.split - 1u : 0u;
+                part0 = u.is_tail ? (u.tail_idx * (tail.split - 1u)) * CTA_GROUP + rank : 0u;   // slice 1 of this tile
+                if (u.is_tail && u.slice > 0) {
+                    // ===== helper: fp32 partial sums to the workspace, then the flag =====
+                    helper = true;
+                    const uint32_t part = part0 + (u.slice - 1u) * CTA_GROUP;
+                    float4 *dst = reinterpret_cast<float4 *>(tail.ws + static_cast<size_t>(part) * kPartFloats) +
+                                  (q * 32u + lane);
 #pragma unroll 1
-                for (uint32_t ch = 0; ch < BN / kStoreCols; ++ch) {
-                    uint32_t v[2][32];
-                    tmem_ld_32x32b_x32(taddr + ch * kStoreCols, v[0]);
-                    tmem_ld_32x32b_x32(taddr + ch * kStoreCols + 32u, v[1]);
-                    tmem_ld_wait();
+                    for (uint32_t ch = 0; ch < BN / kStoreCols; ++ch) {
+                        uint32_t v[2][32];
+                        tmem_ld_32x32b_x32(taddr + ch * kStoreCols, v[0]);
+                        tmem_ld_32x32b_x32(taddr + ch * kStoreCols + 32u, v[1]);
+                        tmem_ld_wait();
 #pragma unroll
-                    for (uint32_t c4 = 0; c4 < 16; ++c4) {      // column group c4 of this chunk: [group][row][4]
-                        const uint32_t *src = &v[c4 >> 3][(c4 & 7u) * 4u];
-                        dst[(ch * 16u + c4) * kBM] = make_float4(__uint_as_float(src[0]), __uint_as_float(src[1]),
-                                                                 __uint_as_float(src[2]), __uint_as_float(src[3]));
+                        for (uint32_t c4 = 0; c4 < 16; ++c4) {      // column group c4 of this chunk: [group][row][4]
+                            const uint32_t *src = &v[c4 >> 3][(c4 & 7u) * 4u];
+                            dst[(ch * 16u + c4) * kBM] = make_float4(__uint_as_float(src[0]), __uint_as_float(src[1]),
+                                                                     __uint_as_float(src[2]), __uint_as_float(src[3]));
+                        }
+                    }
+                    tc_fence_before_sync();
+                    __threadfence();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if constexpr (CTA_GROUP == 2) mbar_arrive_cluster(acc_empty_leader + acc * 8);
+                        else mbar_arrive(bar_acc_empty + acc * 8);
+                        st_release_gpu(tail.flags + part * kEpiWarps + e, 1u);
                     }
                 }
-                tc_fence_before_sync();
-                __threadfence();
-                __syncwarp();
-                if (lane == 0) {
-                    if constexpr (CTA_GROUP == 2) mbar_arrive_cluster(acc_empty_leader + acc * 8);
-                    else mbar_arrive(bar_acc_empty + acc * 8);
-                    st_release_gpu(tail.flags + part * kEpiWarps + e, 1u);
+                if (n_parts) {
+                    // ===== owner: the helpers' partial sums must have landed =====
+                    for (uint32_t j = 0; ok && j < n_parts; ++j)
+                        ok = wait_flag(tail.flags + (part0 + j * CTA_GROUP) * kEpiWarps + e, ctx);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
                 }
-                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
-                continue;
             }
-            if (n_parts) {
-                // ===== owner: the helpers' partial sums must have landed =====
-                for (uint32_t j = 0; ok && j < n_parts; ++j)
-                    ok = wait_flag(tail.flags + (part0 + j * CTA_GROUP) * kEpiWarps + e, ctx);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-            }
+            if (helper) continue;
 #pragma unroll 1
             for (uint32_t ch = 0; ch < BN / kStoreCols; ++ch) {
                 uint32_t v[2][32];
@@ -533,22 +580,24 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                     tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) {
-                        if constexpr (CTA_GROUP == 2) mbar_arrive_cluster(acc_empty_leader + acc * 8);
-                        else mbar_arrive(bar_acc_empty + acc * 8);
+                        if constexpr (CTA_GROUP == 2) mbar_arrive_cluster(acc_empty_leader + a_idx * 8);
+                        else mbar_arrive(bar_acc_empty + a_idx * 8);
                     }
                 }
-                for (uint32_t j = 0; j < n_parts; ++j) {      // slice order: deterministic
-                    const float4 *src = reinterpret_cast<const float4 *>(
-                                            tail.ws + static_cast<size_t>(part0 + j * CTA_GROUP) * kPartFloats) +
-                                        (q * 32u + lane);
+                if constexpr (MT == 1) {
+                    for (uint32_t j = 0; j < n_parts; ++j) {      // slice order: deterministic
+                        const float4 *src = reinterpret_cast<const float4 *>(
+                                                tail.ws + static_cast<size_t>(part0 + j * CTA_GROUP) * kPartFloats) +
+                                            (q * 32u + lane);
 #pragma unroll
-                    for (uint32_t c4 = 0; c4 < 16; ++c4) {
-                        const float4 p = __ldcg(src + (ch * 16u + c4) * kBM);
-                        uint32_t *d = &v[c4 >> 3][(c4 & 7u) * 4u];
-                        d[0] = __float_as_uint(__uint_as_float(d[0]) + p.x);
-                        d[1] = __float_as_uint(__uint_as_float(d[1]) + p.y);
-                        d[2] = __float_as_uint(__uint_as_float(d[2]) + p.z);
-                        d[3] = __float_as_uint(__uint_as_float(d[3]) + p.w);
+                        for (uint32_t c4 = 0; c4 < 16; ++c4) {
+                            const float4 p = __ldcg(src + (ch * 16u + c4) * kBM);
+                            uint32_t *d = &v[c4 >> 3][(c4 & 7u) * 4u];
+                            d[0] = __float_as_uint(__uint_as_float(d[0]) + p.x);
+                            d[1] = __float_as_uint(__uint_as_float(d[1]) + p.y);
+                            d[2] = __float_as_uint(__uint_as_float(d[2]) + p.z);
+                            d[3] = __float_as_uint(__uint_as_float(d[3]) + p.w);
+                        }
                     }
                 }
                 // the store issued two chunks ago from this buffer must have finished reading it
@@ -598,7 +647,13 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                 }
                 nbuf ^= 1u;
             }
-            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            }   // row blocks
+            if (!ok) break;
+            if constexpr (MT == 2) {
+                acc_phase ^= 1u;
+            } else {
+                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            }
         }
         // Shared memory must outlive the stores that read it; their global writes are complete when the grid is.
         // With peer destinations the thread waits for the writes themselves, to stay on the safe side of NVLink.
@@ -1232,10 +1287,10 @@ void plan_tail(int64_t m, int64_t n, int64_t k, int workers, uint32_t *full_tile
 
 namespace {
 
-template <int CTA_GROUP, int BN, int STAGES, bool BF16>
+template <int CTA_GROUP, int BN, int STAGES, int MT, bool BF16>
 cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t stream) {
-    using C = Cfg<CTA_GROUP, BN, STAGES>;
-    auto kernel = hgemm_tcgen05_kernel<CTA_GROUP, BN, STAGES, BF16>;
+    using C = Cfg<CTA_GROUP, BN, STAGES, MT>;
+    auto kernel = hgemm_tcgen05_kernel<CTA_GROUP, BN, STAGES, MT, BF16>;
     static bool attr_done[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1255,14 +1310,14 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
             return cudaErrorInvalidValue;
     const uint32_t n_dst = 1u + static_cast<uint32_t>(g.n_extra_dst);
 
-    const uint32_t tile_m = kBM * CTA_GROUP;
+    const uint32_t tile_m = kBM * CTA_GROUP * MT;
     const uint64_t m_tiles = (g.m + tile_m - 1) / tile_m;
     const uint64_t n_tiles = (g.n + BN - 1) / BN;
     const uint64_t tiles = m_tiles * n_tiles;
     uint64_t workers = static_cast<uint64_t>(sms / CTA_GROUP);
 
     TailArgs tail = {static_cast<uint32_t>(tiles), 0u, nullptr, nullptr};
-    if (CTA_GROUP == 2 && BN == 256 && g.workspace && g.n_extra_dst == 0) {
+    if (CTA_GROUP == 2 && BN == 256 && MT == 1 && g.workspace && g.n_extra_dst == 0) {
         uint32_t full = 0, split = 0;
         size_t need = 0;
         plan_tail(g.m, g.n, g.k, static_cast<int>(workers), &full, &split, &need);
@@ -1292,7 +1347,7 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
     // PEAKGEMM_TUNE_FLAGS (the kFlag* switches).
     static const int env_group_m = getenv("PEAKGEMM_TUNE_GROUP_M") ? atoi(getenv("PEAKGEMM_TUNE_GROUP_M")) : 0;
     static const int env_flags = getenv("PEAKGEMM_TUNE_FLAGS") ? atoi(getenv("PEAKGEMM_TUNE_FLAGS")) : -1;
-    const uint32_t group_m = env_group_m > 0 ? static_cast<uint32_t>(env_group_m) : 16 / CTA_GROUP;
+    const uint32_t group_m = env_group_m > 0 ? static_cast<uint32_t>(env_group_m) : 16 / (CTA_GROUP * MT);
     // one tile row (m <= 128): every weight byte is read exactly once, so B streams through L2 (evict first)
     const uint32_t shape_flags = (CTA_GROUP == 1 && g.m <= 128) ? kFlagBEvictFirst : 0u;
     const uint32_t flags = env_flags >= 0 ? static_cast<uint32_t>(env_flags) : (kDefaultFlags | shape_flags);
@@ -1386,10 +1441,10 @@ int choose_skinny_split(const GemmArgs &g, int sm_count) {
     return best;
 }
 
-template <int CTA_GROUP, int BN, int STAGES>
+template <int CTA_GROUP, int BN, int STAGES, int MT = 1>
 cudaError_t launch_dt(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t stream) {
-    return g.bf16 ? launch<CTA_GROUP, BN, STAGES, true>(g, d, sms, stream)
-                  : launch<CTA_GROUP, BN, STAGES, false>(g, d, sms, stream);
+    return g.bf16 ? launch<CTA_GROUP, BN, STAGES, MT, true>(g, d, sms, stream)
+                  : launch<CTA_GROUP, BN, STAGES, MT, false>(g, d, sms, stream);
 }
 
 }  // namespace
@@ -1399,6 +1454,10 @@ cudaError_t launch_dt(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStrea
 // width, divided by how efficient that configuration is per tile.  (The reference
 // has one fixed configuration: hgemm_wmma_impl.h:410.)
 void choose_config(const GemmArgs &g, int sm_count, int *variant, int *block_n) {
+    if (*variant == 5) {          // two row blocks per CTA exist at one tile width only
+        if (*block_n == 0) *block_n = 256;
+        return;
+    }
     const int v_lo = (*variant == 0) ? 1 : *variant, v_hi = (*variant == 0) ? 2 : *variant;
     double best = 1e300;
     int best_v = v_lo, best_bn = (*block_n == 0) ? 256 : *block_n;
@@ -1563,6 +1622,9 @@ int hgemm_launch(const GemmArgs &g, int variant, int block_n, int max_sms, cudaS
         else if (block_n == 128) e = launch_dt<2, 128, 8>(g, *d, sms, stream);
         else if (block_n == 64) e = launch_dt<2, 64, 8>(g, *d, sms, stream);
         else return kLaunchBadConfig;
+    } else if (variant == 5) {
+        if (block_n != 256 && block_n != 0) return kLaunchBadConfig;
+        e = launch_dt<2, 256, 4, 2>(g, *d, sms, stream);
     } else {
         return kLaunchBadConfig;
     }

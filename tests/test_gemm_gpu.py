@@ -1,8 +1,9 @@
 """GPU parity of the tcgen05 GEMM with the oracle, called through the C ABI (pg_hgemm_ex).
 
-Bound for every case: max|C - C_ref| <= (2e-2 * sqrt(k/4096) + eps_out) * max|C_ref| (C_ref = fp32-accumulated
-product of the same 16-bit inputs; eps_out = one rounding step of the output type), plus the reference test's own bound 0.5*k/4096 against the exact
-k-ordered oracle where that is affordable.  Inputs are generated on the CPU from fixed seeds, C is
+Every case (tests/helpers.py:check_gemm): the acceptance bound max|C - C_ref| <= (2e-2 * sqrt(k/4096) + eps_out) *
+max|C_ref| (C_ref = fp32-accumulated product of the same 16-bit inputs; eps_out = one rounding step of the output
+type); per element, C must be the correctly rounded value of a number within the fp32 accumulation slack of the oracle's
+sum; and, where the exact k-ordered oracle is affordable, the reference test's own bound 0.5*k/4096.  Inputs are generated on the CPU from fixed seeds, C is
 pre-filled with garbage (the reference's tests do the same: test/test_gemm.py:32-34).
 """
 import pytest
@@ -54,6 +55,39 @@ def test_pair_multi_kblock(cuda):
 @pytest.mark.parametrize("dtype", [BF16, F16])
 def test_pair_variants(cuda, block_n, dtype):
     run_case(512, 768, 1024, dtype, 2, block_n, seed=1)
+
+
+# ---- CTA pair with two row blocks per CTA (variant 5): 512 x 256 tiles, both accumulators belong to one tile
+@pytest.mark.parametrize("dtype", [BF16, F16])
+@pytest.mark.parametrize("m,n,k", [
+    (512, 256, 64),        # one tile, one k-block
+    (512, 256, 1024),      # one tile, the ring wraps four times
+    (1024, 768, 512),      # 2 x 3 tiles
+    (4096, 8192, 256),     # 256 tiles on 74 pairs: several tiles per pair, both accumulators drained and refilled
+    (300, 264, 136),       # tails in m (the second row block is partly empty), n and k
+    (260, 520, 72),        # the second row block holds 4 rows
+    (128, 256, 128),       # fewer rows than one row block of the peer CTA
+    (1000, 1000, 1000),
+])
+def test_pair_two_row_blocks(cuda, m, n, k, dtype):
+    run_case(m, n, k, dtype, 5, 0, seed=21, exact=True)
+
+
+def test_pair_two_row_blocks_matches_pair_kernel_bitwise(cuda):
+    """The same k-ordered accumulation per element as the 256 x 256 CTA-pair kernel: identical bits."""
+    from peakgemm_b200 import capi
+
+    a, b = oracle.gemm_inputs_uniform(2048, 2304, 4096, BF16, 22)
+    ad, bd = a.cuda(), b.cuda()
+    c2 = helpers.garbage_like((2048, 2304), BF16, "cuda")
+    c5 = helpers.garbage_like((2048, 2304), BF16, "cuda")
+    capi.hgemm(c2, ad, bd, variant=2, block_n=256)
+    capi.hgemm(c5, ad, bd, variant=5)
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0
+    assert torch.equal(c2.view(torch.int16), c5.view(torch.int16))
+    assert capi.lib().pg_hgemm_ex(ad.data_ptr(), ad.data_ptr(), ad.data_ptr(), 512, 256, 64, 64, 64, 256, 1, 5, 128,
+                                  0, None) == 1      # variant 5 exists at block_n 256 only
 
 
 # ---- cluster split-K (variant 3): 2, 4 or 8 CTAs share a tile and combine partial sums through
@@ -266,14 +300,77 @@ def test_config2_8192_vs_device_oracle(cuda, dtype):
     helpers.check_gemm(c[rows], a[rows], b, exact_rows=False)
 
 
+def full_size_case(m, n, k, dtype, seed, gen, sample_rows=64, exact_rows=4, workspace=True):
+    """A full-size benchmark shape the way the operator runs it (automatic configuration, tail-split workspace
+    when the shape qualifies): every element against the device restatement of the reference's naive kernel,
+    `sample_rows` rows against the CPU oracle (acceptance bound + per-element rounding check) and `exact_rows` of
+    them against the exact k-ordered CPU sum."""
+    from peakgemm_b200 import capi
+
+    a, b = gen(m, n, k, dtype, seed)
+    ad, bd = a.cuda(), b.cuda()
+    c = helpers.garbage_like((m, n), dtype, "cuda")
+    need = capi.hgemm_workspace_bytes(m, n, k) if workspace else 0
+    ws = torch.full((need,), 0xAB, dtype=torch.uint8, device="cuda") if need else None
+    capi.hgemm_ws(c, ad, bd, ws)
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0, "a kernel abandoned a bounded wait"
+    helpers.check_gemm_device(c, ad, bd)
+    rows = (torch.arange(sample_rows) * (m // sample_rows) + 7 * (m > 7 * sample_rows)) % m if m > sample_rows \
+        else torch.arange(m)
+    helpers.check_gemm(c[rows.cuda()], a[rows], b, exact_rows=False)
+    ex = rows[:exact_rows]
+    helpers.check_gemm(c[ex.cuda()], a[ex], b, exact_rows=True)
+    return need
+
+
+@pytest.mark.parametrize("dtype", [BF16, F16])
+def test_config2_16384(cuda, dtype):
+    """benchmark config 2 at its largest size (the reference validates it too: test/cpp/test_gemm_half.cpp:174-192).
+    4096 tiles on 74 SM pairs leave a remainder of 26: the CTA-pair kernel runs with the tail split."""
+    need = full_size_case(16384, 16384, 16384, dtype, 1, oracle.gemm_inputs_uniform)
+    assert need > 0, "16384^3 is expected to take the tail split on a 148-SM device"
+
+
 @pytest.mark.parametrize("m", [16, 128, 1024])
 @pytest.mark.parametrize("n,k", [(4096, 4096), (14336, 4096), (4096, 14336)])
 def test_config3_skinny(cuda, m, n, k):
     run_case(m, n, k, BF16, 0, 0, seed=2, gen=oracle.gemm_inputs_llm, exact=False)
 
 
-def test_config3_vocab_projection(cuda):
-    run_case(128, 128256, 4096, BF16, 0, 0, seed=2, gen=oracle.gemm_inputs_llm, exact=False)
+@pytest.mark.parametrize("n,k", [(4096, 4096), (14336, 4096), (4096, 14336), (128256, 4096)])
+def test_config3_m4096(cuda, n, k):
+    """benchmark config 3 at m = 4096, all four (n, k)."""
+    full_size_case(4096, n, k, BF16, 2, oracle.gemm_inputs_llm, sample_rows=32)
+
+
+@pytest.mark.parametrize("m", [16, 128, 1024])
+def test_config3_vocab_projection(cuda, m):
+    """benchmark config 3 at (n, k) = (128256, 4096) for the remaining m (m = 4096: test_config3_m4096)."""
+    full_size_case(m, 128256, 4096, BF16, 2, oracle.gemm_inputs_llm, sample_rows=16)
+
+
+def test_config5_per_rank_block(cuda):
+    """benchmark config 5 as one of 8 ranks sees it: m = 32768, k = 16384, its 4096 columns of B (seed 4), written
+    as a column block into a wider C (ldc > n) the way the column-sharded caller does."""
+    from peakgemm_b200 import capi
+
+    m, n_local, k, ldc = 32768, 4096, 16384, 8192
+    g = torch.Generator().manual_seed(4)
+    a = (torch.rand(m, k, generator=g) * 2 - 1).to(BF16)
+    b = (torch.rand(n_local, k, generator=g) * 2 - 1).to(BF16)       # the first rank's rows of B
+    ad, bd = a.cuda(), b.cuda()
+    wide = helpers.garbage_like((m, ldc), BF16, "cuda")
+    before = wide[:, :n_local].clone()
+    block = wide[:, n_local:]
+    capi.hgemm(block, ad, bd, ldc=ldc)
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0
+    assert torch.equal(wide[:, :n_local], before), "columns outside the block were written"
+    helpers.check_gemm_device(block, ad, bd)
+    rows = torch.arange(32) * 1024 + 11
+    helpers.check_gemm(block[rows.cuda()], a[rows], b, exact_rows=False)
+    helpers.check_gemm(block[rows[:4].cuda()], a[rows[:4]], b, exact_rows=True)
 
 
 # ---- size-independent properties at full size
