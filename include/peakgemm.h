@@ -210,7 +210,7 @@ int pg_peer_last_cuda_error(void);
 
 /*
  * The configuration pg_hgemm would choose for this shape on a device with
- * sm_count SMs: writes variant (1 or 2) and block_n (64, 128, 256).  Pure host
+ * sm_count SMs: writes variant (1, 2 or 5) and block_n (64, 128, 256).  Pure host
  * arithmetic, needs no GPU.  (The reference's counterpart is the fixed
  * instantiation at hgemm_wmma_impl.h:410,421.)
  */
@@ -219,8 +219,15 @@ int pg_hgemm_config(int64_t m, int64_t n, int64_t k, int sm_count, int *variant,
 /*
  * Device-side status word of the kernels on the current device: 0 if no kernel
  * has given up on a bounded wait since the last call, otherwise a code that names
- * the waiting role (1-4: GEMM producer / MMA / epilogue; 11-12: RMSNorm).  Synchronises `stream`, reads the word, clears
- * it.  Returns PG_OK and writes *device_status, or an error status.
+ * the waiting role (1-5: GEMM producer / MMA / epilogue; 11-12: RMSNorm).
+ * Synchronises `stream`, reads the word, clears it and writes it to
+ * *device_status.  Returns PG_OK when the word was 0, PG_ERR_DEVICE_TIMEOUT when a
+ * kernel had given up (the output of that launch is then incomplete; the context
+ * stays usable and later launches are unaffected), or another error status.
+ * The word belongs to the DEVICE, not to a stream: kernels of every stream report
+ * into it and a read clears it, so poll from ONE place per device, after the
+ * streams of interest have been synchronised; two pollers would take each
+ * other's codes.
  */
 int pg_device_status(int *device_status, void *stream);
 
@@ -293,6 +300,9 @@ int pg_rmsnorm_bwd(void *dx, float *dgamma, const void *dy, const void *x,
  *    whose kernels overlap on the GPU — different streams, no ordering between
  *    them — race on it and corrupt each other's dgamma.  Serialise them, or use
  *    pg_rmsnorm_bwd with separate workspaces.
+ *  - The looked-up device address is cached per device ordinal for the life of
+ *    the process; it assumes the device's primary context is not reset
+ *    (cudaDeviceReset) between calls.
  */
 #define PG_STATIC_SCRATCH_BYTES (160u * 8192u * 4u)
 int pg_rmsnorm_bwd_static(void *dx, float *dgamma, const void *dy, const void *x,
@@ -307,8 +317,10 @@ int pg_rmsnorm_bwd_static(void *dx, float *dgamma, const void *dy, const void *x
  * back to back on pseudo-random operand tiles resident in shared memory, `iters`
  * rounds of k = 64, no loads in the loop; writes the TFLOP/s reached (and the
  * milliseconds).  Synchronises the device's default stream; allocates nothing.
+ * 1 <= iters <= PG_PROBE_MAX_ITERS (about 0.4 s of MMAs; PG_ERR_BAD_ARG beyond).
  * pg_probe_copy: 128-bit streaming copy, asynchronous on `stream`.
  */
+#define PG_PROBE_MAX_ITERS (1 << 20)
 int pg_probe_tensor_peak(int dtype, int iters, float *tflops_out, float *ms_out);
 int pg_probe_copy(void *dst, const void *src, size_t bytes, void *stream);
 

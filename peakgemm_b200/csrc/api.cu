@@ -6,6 +6,7 @@
 
 #include "../../include/peakgemm.h"
 #include "gemm_sm100.h"
+#include "host_util.h"
 #include "rmsnorm.h"
 #include "sgemm.h"
 
@@ -33,6 +34,10 @@ int from_launch(int r, cudaError_t e) {
 constexpr int64_t kMaxDim = (int64_t(1) << 31) - 1;
 
 }  // namespace
+
+namespace pg {
+int record_cuda_failure(cudaError_t e) { return cuda_fail(e); }
+}  // namespace pg
 
 extern "C" {
 
@@ -77,21 +82,12 @@ int pg_hgemm_ex(void *c, const void *a, const void *b, int64_t m, int64_t n, int
 
 size_t pg_hgemm_workspace_bytes(int64_t m, int64_t n, int64_t k) {
     if (m <= 0 || n <= 0 || k <= 0) return 0;
-    static int sm_count[64] = {};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    int sms = 0;
+    if (pg::current_device_sm_count(&sms) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
-    if (sm_count[dev] == 0) {
-        int n_sm = 0;
-        if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
-            cudaGetLastError();
-            return 0;
-        }
-        sm_count[dev] = n_sm;
-    }
-    return pg::hgemm_workspace_bytes(m, n, k, sm_count[dev]);
+    return pg::hgemm_workspace_bytes(m, n, k, sms);
 }
 
 int pg_hgemm_ws(void *c, const void *a, const void *b, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb,
@@ -214,7 +210,7 @@ int pg_device_status(int *device_status, void *stream) {
     e = pg::rmsnorm_device_status(&rms, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(e);
     *device_status = gemm != 0 ? gemm : rms;
-    return PG_OK;
+    return *device_status != 0 ? PG_ERR_DEVICE_TIMEOUT : PG_OK;
 }
 
 int pg_rmsnorm_fwd(void *y, const void *x, const float *gamma, int64_t rows, int64_t h, float eps,

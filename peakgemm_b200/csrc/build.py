@@ -8,7 +8,10 @@ The reference project builds the same pair with CMake (CMakeLists.txt:11-40:
 `${PROJECT}` MODULE from src/register.cpp).  Here the architecture is fixed to
 sm_100a (`-arch native` needs a visible GPU) and torch headers never reach nvcc.
 
-    python peakgemm_b200/csrc/build.py [--force] [--verbose]
+    python peakgemm_b200/csrc/build.py [--force] [--verbose] [--tuning]
+
+--tuning compiles the benchmark-only PEAKGEMM_TUNE_* environment overrides in (-DPG_ENABLE_TUNING); the
+library is shipped without them and then never reads the environment.
 
 Run as a script (or loaded by path): it must work before the package can be
 imported, because importing the package requires the built libraries.
@@ -29,7 +32,7 @@ DEVICE_LIB = os.path.join(PKG_DIR, "libPeakGemm_device.so")
 TORCH_LIB = os.path.join(PKG_DIR, "libPeakGemm.so")
 
 DEVICE_SOURCES = ["gemm_sm100.cu", "rmsnorm.cu", "rmsnorm_staged.cu", "rmsnorm_static.cu", "rmsnorm_rstd.cu", "peer.cu", "sgemm.cu", "probes.cu", "api.cu"]
-DEVICE_HEADERS = ["ptx.cuh", "gemm_sm100.h", "rmsnorm.h", "sgemm.h", os.path.join(INCLUDE, "peakgemm.h")]
+DEVICE_HEADERS = ["ptx.cuh", "gemm_sm100.h", "host_util.h", "rmsnorm.h", "sgemm.h", os.path.join(INCLUDE, "peakgemm.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -66,7 +69,7 @@ def _run(cmd: list[str], verbose: bool) -> None:
         print(r.stdout, r.stderr, flush=True)
 
 
-def build_device_lib(force: bool = False, verbose: bool = False) -> str:
+def build_device_lib(force: bool = False, verbose: bool = False, tuning: bool = False) -> str:
     srcs = [os.path.join(CSRC, s) for s in DEVICE_SOURCES]
     hdrs = [h if os.path.isabs(h) else os.path.join(CSRC, h) for h in DEVICE_HEADERS]
     if not force and _newer(DEVICE_LIB, srcs + hdrs):
@@ -78,7 +81,7 @@ def build_device_lib(force: bool = False, verbose: bool = False) -> str:
     for s in srcs:
         o = os.path.join(obj_dir, os.path.basename(s) + ".o")
         objs.append(o)
-        cmd = [_nvcc(), *NVCC_FLAGS, "-I", INCLUDE, "-c", s, "-o", o]
+        cmd = [_nvcc(), *NVCC_FLAGS, *(["-DPG_ENABLE_TUNING"] if tuning else []), "-I", INCLUDE, "-c", s, "-o", o]
         if verbose:
             print("+", " ".join(cmd), flush=True)
         procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
@@ -112,10 +115,10 @@ def build_torch_lib(force: bool = False, verbose: bool = False) -> str:
     return TORCH_LIB
 
 
-def build_all(force: bool = False, verbose: bool = False) -> tuple[str, str]:
-    return build_device_lib(force, verbose), build_torch_lib(force, verbose)
+def build_all(force: bool = False, verbose: bool = False, tuning: bool = False) -> tuple[str, str]:
+    return build_device_lib(force or tuning, verbose, tuning), build_torch_lib(force, verbose)
 
 
 if __name__ == "__main__":
-    libs = build_all(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    libs = build_all(force="--force" in sys.argv, verbose="--verbose" in sys.argv, tuning="--tuning" in sys.argv)
     print("\n".join(libs))

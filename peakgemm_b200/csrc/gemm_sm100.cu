@@ -67,6 +67,7 @@
 #include <stdlib.h>
 
 #include "gemm_sm100.h"
+#include "host_util.h"
 #include "ptx.cuh"
 
 namespace pg {
@@ -80,6 +81,10 @@ constexpr uint32_t kBK = 64;            // k elements per stage = one 128-byte s
 constexpr uint32_t kUmmaK = 16;         // k elements per tcgen05.mma (16-bit inputs)
 constexpr uint32_t kThreads = 192;
 constexpr uint32_t kEpiWarps = 4;
+// The two-row-block kernel (MT == 2) runs 8 epilogue warps: two per tensor-memory lane quarter, each holding
+// 128 columns of one accumulator in registers, so that an accumulator is handed back after ONE round of loads.
+constexpr uint32_t kEpiWarpsWide = 8;
+constexpr uint32_t kThreadsWide = 64 + 32 * kEpiWarpsWide;
 constexpr uint32_t kStoreCols = 64;     // columns per TMA store box (128 bytes)
 constexpr uint32_t kStoreRows = 32;     // rows per TMA store box (one warp's lanes)
 constexpr uint32_t kStageBufBytes = kStoreRows * kStoreCols * 2;  // 4096
@@ -95,6 +100,7 @@ enum : uint32_t {
     kFlagBEvictFirst = 8u,       // B loads carry an L2 evict-first hint (B streams through once per band)
     kFlagBEvictLast = 16u,       // B loads carry an L2 evict-last hint
     kFlagSerpentine = 32u,       // odd bands walk their columns right to left
+    kFlagRasterAlongN = 64u,     // bands of group_m tile COLUMNS walked row by row: consecutive workers share an A panel
 };
 
 // Codes written to the device status word (role that gave up).
@@ -206,7 +212,7 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, const Wa
             if (t0 == 0) t0 = now;
             else if (now - t0 > kWaitTimeoutNs) {
                 *ctx.abort_flag = 1;
-                atomicCAS(ctx.status, 0, code);
+                if (ctx.status) atomicCAS(ctx.status, 0, code);
                 return false;
             }
         }
@@ -217,6 +223,18 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, const Wa
 // of kGroupM tile rows first, then across the columns, band after band.
 __device__ __forceinline__ void tile_coords(uint32_t kGroupM, uint32_t t, uint32_t m_tiles, uint32_t n_tiles,
                                             uint32_t &mi, uint32_t &ni, bool serpentine = false) {
+    if (kGroupM & 0x10000u) {        // kFlagRasterAlongN folded into the argument: the same walk with m and n swapped
+        const uint32_t g = kGroupM & 0xffffu;
+        const uint32_t per_band = g * m_tiles;
+        const uint32_t band = t / per_band;
+        const uint32_t first_n = band * g;
+        const uint32_t band_cols = min(g, n_tiles - first_n);
+        const uint32_t r = t - band * per_band;
+        ni = first_n + r % band_cols;
+        mi = r / band_cols;
+        if (serpentine && (band & 1u)) mi = m_tiles - 1 - mi;
+        return;
+    }
     const uint32_t per_band = kGroupM * n_tiles;
     const uint32_t band = t / per_band;
     const uint32_t first_m = band * kGroupM;
@@ -297,7 +315,7 @@ __device__ __forceinline__ bool wait_flag(const uint32_t *flag, const WaitCtx &c
             if (t0 == 0) t0 = now;
             else if (now - t0 > kWaitTimeoutNs) {
                 *ctx.abort_flag = 1;
-                atomicCAS(ctx.status, 0, static_cast<int>(kStEpiTailFlag));
+                if (ctx.status) atomicCAS(ctx.status, 0, static_cast<int>(kStEpiTailFlag));
                 return false;
             }
         }
@@ -306,7 +324,7 @@ __device__ __forceinline__ bool wait_flag(const uint32_t *flag, const WaitCtx &c
 }
 
 template <int CTA_GROUP, int BN, int STAGES, int MT, bool BF16>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(MT == 2 ? kThreadsWide : kThreads, 1)
 hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                      const __grid_constant__ CUtensorMap tm_b,
                      const __grid_constant__ DstMaps tm_c, uint32_t n_dst,
@@ -339,6 +357,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
     const uint32_t n_tiles = (N + BN - 1) / BN;
     const uint32_t k_blocks = (K + kBK - 1) / kBK;
     const uint32_t total_tiles = m_tiles * n_tiles;
+    if (flags & kFlagRasterAlongN) group_m |= 0x10000u;   // tile_coords reads the raster direction from here
     const uint32_t worker = blockIdx.x / CTA_GROUP;       // cluster index (CTA index when CTA_GROUP == 1)
     const uint32_t workers = gridDim.x / CTA_GROUP;
 
@@ -350,7 +369,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         }
         for (uint32_t a = 0; a < 2; ++a) {
             mbar_init(bar_acc_full + a * 8, 1);                          // tcgen05.commit / relay
-            mbar_init(bar_acc_empty + a * 8, kEpiWarps * CTA_GROUP);     // one arrive per epilogue warp
+            mbar_init(bar_acc_empty + a * 8, (MT == 2 ? kEpiWarpsWide : kEpiWarps) * CTA_GROUP);   // one arrive per epilogue warp
         }
         *abort_flag = 0;
         fence_mbar_init();
@@ -490,61 +509,146 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         }
         __syncwarp();
     } else {
-        // ===== epilogue =====
-        const uint32_t q = warp & 3u;                 // lane quarter this warp may read
-        const uint32_t e = warp - 2u;                 // 0..3: staging buffers
-        const uint32_t buf0 = smem_base + C::kOffC + e * 2 * kStageBufBytes;
-        uint8_t *buf0_gen = smem_gen + C::kOffC + e * 2 * kStageBufBytes;
-        const uint32_t acc_empty_leader = (CTA_GROUP == 2) ? mapa(bar_acc_empty, 0) : bar_acc_empty;
-        const uint32_t peer_acc_full = (CTA_GROUP == 2) ? mapa(bar_acc_full, 1) : 0u;
-        uint32_t acc = 0, acc_phase = 0, nbuf = 0;
-        bool ok = true;
-        const uint64_t pol_store = l2_policy_evict_first();
-        for (uint32_t it = 0; ok; ++it) {
-            const Unit u = unit_at(it, worker, workers, total_tiles, k_blocks, tail);
-            if (!u.valid) break;
-            uint32_t mi, ni;
-            tile_coords(group_m, u.tile, m_tiles, n_tiles, mi, ni, (flags & kFlagSerpentine) != 0);
-            // All 32 lanes probe: a failed try_wait parks the warp in hardware, so this costs nothing (a
-            // one-lane poll with __nanosleep back-off executed 40 % MORE instructions and ran 0.7 % slower).
-            constexpr uint32_t acc_full_slot = 0;   // MT == 2 signals on slot 0 only
-            const uint32_t full_bar = (MT == 2) ? bar_acc_full + acc_full_slot * 8 : bar_acc_full + acc * 8;
-            ok = wait_bar(full_bar, acc_phase, ctx, kStEpiAccFull);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            if constexpr (CTA_GROUP == 2) {
-                if (leader && e == 0 && lane == 0)
-                    mbar_arrive_cluster(peer_acc_full + ((MT == 2) ? 0u : acc) * 8);  // relay
-            }
-            tc_fence_after_sync();
+        if constexpr (MT == 2) {
+            // ===== epilogue, two row blocks per CTA: 8 warps =====
+            // Warp w reads lane quarter w % 4 (the hardware rule) and column half (w - 2) / 4 of each accumulator:
+            // 32 rows x 128 columns = 128 registers per thread.  One round of loads empties an accumulator; it goes
+            // back to the MMA warp before anything is converted or stored, accumulator 0 first, so the next tile's
+            // first row block restarts while accumulator 1 is still being read.
+            const uint32_t q = warp & 3u;
+            const uint32_t e = warp - 2u;                 // 0..7: one 32 x 64 staging box each
+            const uint32_t half = e >> 2;                 // columns [128 * half, 128 * half + 128)
+            const uint32_t sbuf = smem_base + C::kOffC + e * kStageBufBytes;
+            uint8_t *sbuf_gen = smem_gen + C::kOffC + e * kStageBufBytes;
+            const uint32_t acc_empty_leader = mapa(bar_acc_empty, 0);
+            const uint32_t peer_acc_full = mapa(bar_acc_full, 1);
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            const uint64_t pol_store = l2_policy_evict_first();
             const bool fused = epi.any();
-#pragma unroll 1
-            for (uint32_t mt = 0; mt < MT; ++mt) {
-            const uint32_t a_idx = (MT == 2) ? mt : acc;                // accumulator read here
-            const uint32_t row0 = mi * kTileM + mt * kBlockM + rank * kBM + q * 32u;   // first row of this warp's slab
-            const uint32_t taddr = tmem_base + a_idx * BN + ((q * 32u) << 16);
-            const bool row_ok = row0 + lane < M;
-            const float rs = fused ? epi_row_scale(epi, row_ok, row0 + lane) : 1.f;
-            // k-slices of a remainder tile: where this warp's rows of slice j live in the workspace, and its flag
-            constexpr uint32_t kPartFloats = kBM * BN;                  // one CTA's partial tile
-            uint32_t n_parts = 0, part0 = 0;
-            bool helper = false;
-            if constexpr (MT == 1) {
-                n_parts = (u.is_tail && u.slice == 0) ? tail.split - 1u : 0u;
-                part0 = u.is_tail ? (u.tail_idx * (tail.split - 1u)) * CTA_GROUP + rank : 0u;   // slice 1 of this tile
+            for (uint32_t it = 0; ok; ++it) {
+                const Unit u = unit_at(it, worker, workers, total_tiles, k_blocks, tail);
+                if (!u.valid) break;
+                uint32_t mi, ni;
+                tile_coords(group_m, u.tile, m_tiles, n_tiles, mi, ni, (flags & kFlagSerpentine) != 0);
+                ok = wait_bar(bar_acc_full, acc_phase, ctx, kStEpiAccFull);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                if (leader && e == 0 && lane == 0) mbar_arrive_cluster(peer_acc_full);   // relay to the peer CTA
+                tc_fence_after_sync();
+    #pragma unroll 1
+                for (uint32_t mt = 0; mt < 2; ++mt) {
+                    const uint32_t row0 = mi * kTileM + mt * kBlockM + rank * kBM + q * 32u;
+                    const uint32_t taddr = tmem_base + mt * BN + half * 128u + ((q * 32u) << 16);
+                    uint32_t v[4][32];
+                    tmem_ld_32x32b_x32(taddr, v[0]);
+                    tmem_ld_32x32b_x32(taddr + 32u, v[1]);
+                    tmem_ld_32x32b_x32(taddr + 64u, v[2]);
+                    tmem_ld_32x32b_x32(taddr + 96u, v[3]);
+                    tmem_ld_wait();
+                    // this warp's part of accumulator mt is in registers: hand it back
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(acc_empty_leader + mt * 8);
+                    const bool row_ok = row0 + lane < M;
+                    const float rs = fused ? epi_row_scale(epi, row_ok, row0 + lane) : 1.f;
+    #pragma unroll
+                    for (uint32_t cb = 0; cb < 2; ++cb) {       // two 32 x 64 boxes
+                        const uint32_t col0 = ni * BN + half * 128u + cb * kStoreCols;
+                        if (fused) {
+    #pragma unroll
+                            for (uint32_t c = 0; c < 8; ++c) {
+                                if (col0 + c * 8u < N) {      // n is a multiple of 8: a group of 8 columns is in or out
+                                    float f[8];
+    #pragma unroll
+                                    for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[2 * cb + (c >> 2)][(c & 3u) * 8u + i]);
+                                    epi_apply8<BF16>(f, rs, epi, row_ok, row0 + lane, col0 + c * 8u);
+    #pragma unroll
+                                    for (int i = 0; i < 8; ++i) v[2 * cb + (c >> 2)][(c & 3u) * 8u + i] = __float_as_uint(f[i]);
+                                }
+                            }
+                        }
+                        uint4 o[8];
+    #pragma unroll
+                        for (uint32_t c = 0; c < 8; ++c) {
+                            const uint32_t *src = &v[2 * cb + (c >> 2)][(c & 3u) * 8u];
+                            o[c].x = pack2<BF16>(__uint_as_float(src[0]), __uint_as_float(src[1]));
+                            o[c].y = pack2<BF16>(__uint_as_float(src[2]), __uint_as_float(src[3]));
+                            o[c].z = pack2<BF16>(__uint_as_float(src[4]), __uint_as_float(src[5]));
+                            o[c].w = pack2<BF16>(__uint_as_float(src[6]), __uint_as_float(src[7]));
+                        }
+                        // the previous store from this box must have finished reading it
+                        if (lane == 0) bulk_wait_group_read<0>();
+                        __syncwarp();
+                        // row `lane`, 8 chunks of 16 bytes, chunk c stored at position c ^ (row % 8)  (128-byte swizzle)
+    #pragma unroll
+                        for (uint32_t c = 0; c < 8; ++c)
+                            *reinterpret_cast<uint4 *>(sbuf_gen + lane * 128u + ((c ^ (lane & 7u)) << 4)) = o[c];
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (row0 < M && col0 < N) {
+                                for (uint32_t d = 0; d < n_dst; ++d) {
+                                    if (flags & kFlagStoreEvictFirst)
+                                        tma_store_2d_hint(&tm_c.m[d], sbuf, static_cast<int32_t>(col0),
+                                                          static_cast<int32_t>(row0), pol_store);
+                                    else
+                                        tma_store_2d(&tm_c.m[d], sbuf, static_cast<int32_t>(col0),
+                                                     static_cast<int32_t>(row0));
+                                }
+                            }
+                            bulk_commit_group();
+                        }
+                    }
+                }
+                acc_phase ^= 1u;
+            }
+        } else {
+            // ===== epilogue =====
+            const uint32_t q = warp & 3u;                 // lane quarter this warp may read
+            const uint32_t e = warp - 2u;                 // 0..3: staging buffers
+            const uint32_t buf0 = smem_base + C::kOffC + e * 2 * kStageBufBytes;
+            uint8_t *buf0_gen = smem_gen + C::kOffC + e * 2 * kStageBufBytes;
+            const uint32_t acc_empty_leader = (CTA_GROUP == 2) ? mapa(bar_acc_empty, 0) : bar_acc_empty;
+            const uint32_t peer_acc_full = (CTA_GROUP == 2) ? mapa(bar_acc_full, 1) : 0u;
+            uint32_t acc = 0, acc_phase = 0, nbuf = 0;
+            bool ok = true;
+            const uint64_t pol_store = l2_policy_evict_first();
+            for (uint32_t it = 0; ok; ++it) {
+                const Unit u = unit_at(it, worker, workers, total_tiles, k_blocks, tail);
+                if (!u.valid) break;
+                uint32_t mi, ni;
+                tile_coords(group_m, u.tile, m_tiles, n_tiles, mi, ni, (flags & kFlagSerpentine) != 0);
+                // All 32 lanes probe: a failed try_wait parks the warp in hardware, so this costs nothing (a
+                // one-lane poll with __nanosleep back-off executed 40 % MORE instructions and ran 0.7 % slower).
+                ok = wait_bar(bar_acc_full + acc * 8, acc_phase, ctx, kStEpiAccFull);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                if constexpr (CTA_GROUP == 2) {
+                    if (leader && e == 0 && lane == 0) mbar_arrive_cluster(peer_acc_full + acc * 8);  // relay
+                }
+                tc_fence_after_sync();
+                const uint32_t row0 = mi * kTileM + rank * kBM + q * 32u;   // first row of this warp's slab
+                const uint32_t taddr = tmem_base + acc * BN + ((q * 32u) << 16);
+                const bool fused = epi.any();
+                const bool row_ok = row0 + lane < M;
+                const float rs = fused ? epi_row_scale(epi, row_ok, row0 + lane) : 1.f;
+                // k-slices of a remainder tile: where this warp's rows of slice j live in the workspace, and its flag
+                constexpr uint32_t kPartFloats = kBM * BN;                  // one CTA's partial tile
+                const uint32_t n_parts = (u.is_tail && u.slice == 0) ? tail.split - 1u : 0u;
+                const uint32_t part0 = u.is_tail ? (u.tail_idx * (tail.split - 1u)) * CTA_GROUP + rank : 0u;   // slice 1 of this tile
                 if (u.is_tail && u.slice > 0) {
                     // ===== helper: fp32 partial sums to the workspace, then the flag =====
-                    helper = true;
                     const uint32_t part = part0 + (u.slice - 1u) * CTA_GROUP;
                     float4 *dst = reinterpret_cast<float4 *>(tail.ws + static_cast<size_t>(part) * kPartFloats) +
                                   (q * 32u + lane);
-#pragma unroll 1
+    #pragma unroll 1
                     for (uint32_t ch = 0; ch < BN / kStoreCols; ++ch) {
                         uint32_t v[2][32];
                         tmem_ld_32x32b_x32(taddr + ch * kStoreCols, v[0]);
                         tmem_ld_32x32b_x32(taddr + ch * kStoreCols + 32u, v[1]);
                         tmem_ld_wait();
-#pragma unroll
+    #pragma unroll
                         for (uint32_t c4 = 0; c4 < 16; ++c4) {      // column group c4 of this chunk: [group][row][4]
                             const uint32_t *src = &v[c4 >> 3][(c4 & 7u) * 4u];
                             dst[(ch * 16u + c4) * kBM] = make_float4(__uint_as_float(src[0]), __uint_as_float(src[1]),
@@ -559,6 +663,8 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                         else mbar_arrive(bar_acc_empty + acc * 8);
                         st_release_gpu(tail.flags + part * kEpiWarps + e, 1u);
                     }
+                    if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+                    continue;
                 }
                 if (n_parts) {
                     // ===== owner: the helpers' partial sums must have landed =====
@@ -567,29 +673,26 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                 }
-            }
-            if (helper) continue;
-#pragma unroll 1
-            for (uint32_t ch = 0; ch < BN / kStoreCols; ++ch) {
-                uint32_t v[2][32];
-                tmem_ld_32x32b_x32(taddr + ch * kStoreCols, v[0]);
-                tmem_ld_32x32b_x32(taddr + ch * kStoreCols + 32u, v[1]);
-                tmem_ld_wait();
-                if (ch == BN / kStoreCols - 1) {
-                    // every tcgen05.ld of this accumulator has completed: give it back to the MMA warp
-                    tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) {
-                        if constexpr (CTA_GROUP == 2) mbar_arrive_cluster(acc_empty_leader + a_idx * 8);
-                        else mbar_arrive(bar_acc_empty + a_idx * 8);
+    #pragma unroll 1
+                for (uint32_t ch = 0; ch < BN / kStoreCols; ++ch) {
+                    uint32_t v[2][32];
+                    tmem_ld_32x32b_x32(taddr + ch * kStoreCols, v[0]);
+                    tmem_ld_32x32b_x32(taddr + ch * kStoreCols + 32u, v[1]);
+                    tmem_ld_wait();
+                    if (ch == BN / kStoreCols - 1) {
+                        // every tcgen05.ld of this accumulator has completed: give it back to the MMA warp
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if constexpr (CTA_GROUP == 2) mbar_arrive_cluster(acc_empty_leader + acc * 8);
+                            else mbar_arrive(bar_acc_empty + acc * 8);
+                        }
                     }
-                }
-                if constexpr (MT == 1) {
                     for (uint32_t j = 0; j < n_parts; ++j) {      // slice order: deterministic
                         const float4 *src = reinterpret_cast<const float4 *>(
                                                 tail.ws + static_cast<size_t>(part0 + j * CTA_GROUP) * kPartFloats) +
                                             (q * 32u + lane);
-#pragma unroll
+    #pragma unroll
                         for (uint32_t c4 = 0; c4 < 16; ++c4) {
                             const float4 p = __ldcg(src + (ch * 16u + c4) * kBM);
                             uint32_t *d = &v[c4 >> 3][(c4 & 7u) * 4u];
@@ -599,59 +702,53 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                             d[3] = __float_as_uint(__uint_as_float(d[3]) + p.w);
                         }
                     }
-                }
-                // the store issued two chunks ago from this buffer must have finished reading it
-                if (lane == 0) bulk_wait_group_read<1>();
-                __syncwarp();
-                const uint32_t sbuf = buf0 + nbuf * kStageBufBytes;
-                uint8_t *sbuf_gen = buf0_gen + nbuf * kStageBufBytes;
-                const uint32_t col0 = ni * BN + ch * kStoreCols;
-                if (fused) {
-#pragma unroll
+                    // the store issued two chunks ago from this buffer must have finished reading it
+                    if (lane == 0) bulk_wait_group_read<1>();
+                    __syncwarp();
+                    const uint32_t sbuf = buf0 + nbuf * kStageBufBytes;
+                    uint8_t *sbuf_gen = buf0_gen + nbuf * kStageBufBytes;
+                    const uint32_t col0 = ni * BN + ch * kStoreCols;
+                    if (fused) {
+    #pragma unroll
+                        for (uint32_t c = 0; c < 8; ++c) {
+                            if (col0 + c * 8u < N) {      // n is a multiple of 8: a group of 8 columns is in or out
+                                float f[8];
+    #pragma unroll
+                                for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[c >> 2][(c & 3u) * 8u + i]);
+                                epi_apply8<BF16>(f, rs, epi, row_ok, row0 + lane, col0 + c * 8u);
+    #pragma unroll
+                                for (int i = 0; i < 8; ++i) v[c >> 2][(c & 3u) * 8u + i] = __float_as_uint(f[i]);
+                            }
+                        }
+                    }
+                    // row `lane`, 8 chunks of 16 bytes, chunk c stored at position c ^ (row % 8)  (128-byte swizzle)
+    #pragma unroll
                     for (uint32_t c = 0; c < 8; ++c) {
-                        if (col0 + c * 8u < N) {      // n is a multiple of 8: a group of 8 columns is in or out
-                            float f[8];
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[c >> 2][(c & 3u) * 8u + i]);
-                            epi_apply8<BF16>(f, rs, epi, row_ok, row0 + lane, col0 + c * 8u);
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) v[c >> 2][(c & 3u) * 8u + i] = __float_as_uint(f[i]);
-                        }
+                        const uint32_t *src = &v[c >> 2][(c & 3u) * 8u];
+                        uint4 o;
+                        o.x = pack2<BF16>(__uint_as_float(src[0]), __uint_as_float(src[1]));
+                        o.y = pack2<BF16>(__uint_as_float(src[2]), __uint_as_float(src[3]));
+                        o.z = pack2<BF16>(__uint_as_float(src[4]), __uint_as_float(src[5]));
+                        o.w = pack2<BF16>(__uint_as_float(src[6]), __uint_as_float(src[7]));
+                        *reinterpret_cast<uint4 *>(sbuf_gen + lane * 128u + ((c ^ (lane & 7u)) << 4)) = o;
                     }
-                }
-                // row `lane`, 8 chunks of 16 bytes, chunk c stored at position c ^ (row % 8)  (128-byte swizzle)
-#pragma unroll
-                for (uint32_t c = 0; c < 8; ++c) {
-                    const uint32_t *src = &v[c >> 2][(c & 3u) * 8u];
-                    uint4 o;
-                    o.x = pack2<BF16>(__uint_as_float(src[0]), __uint_as_float(src[1]));
-                    o.y = pack2<BF16>(__uint_as_float(src[2]), __uint_as_float(src[3]));
-                    o.z = pack2<BF16>(__uint_as_float(src[4]), __uint_as_float(src[5]));
-                    o.w = pack2<BF16>(__uint_as_float(src[6]), __uint_as_float(src[7]));
-                    *reinterpret_cast<uint4 *>(sbuf_gen + lane * 128u + ((c ^ (lane & 7u)) << 4)) = o;
-                }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) {
-                    if (row0 < M && col0 < N) {
-                        for (uint32_t d = 0; d < n_dst; ++d) {
-                            if (flags & kFlagStoreEvictFirst)
-                                tma_store_2d_hint(&tm_c.m[d], sbuf, static_cast<int32_t>(col0),
-                                                  static_cast<int32_t>(row0), pol_store);
-                            else
-                                tma_store_2d(&tm_c.m[d], sbuf, static_cast<int32_t>(col0),
-                                             static_cast<int32_t>(row0));
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (row0 < M && col0 < N) {
+                            for (uint32_t d = 0; d < n_dst; ++d) {
+                                if (flags & kFlagStoreEvictFirst)
+                                    tma_store_2d_hint(&tm_c.m[d], sbuf, static_cast<int32_t>(col0),
+                                                      static_cast<int32_t>(row0), pol_store);
+                                else
+                                    tma_store_2d(&tm_c.m[d], sbuf, static_cast<int32_t>(col0),
+                                                 static_cast<int32_t>(row0));
+                            }
                         }
+                        bulk_commit_group();
                     }
-                    bulk_commit_group();
+                    nbuf ^= 1u;
                 }
-                nbuf ^= 1u;
-            }
-            }   // row blocks
-            if (!ok) break;
-            if constexpr (MT == 2) {
-                acc_phase ^= 1u;
-            } else {
                 if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
             }
         }
@@ -1189,7 +1286,6 @@ bool make_tmap(CUtensorMap *tm, const void *base, int64_t rows, int64_t cols, in
 }
 
 struct DeviceInfo {
-    bool ready = false;
     int sm_count = 0;
     int cc_major = 0;
     int *status_word = nullptr;
@@ -1197,25 +1293,30 @@ struct DeviceInfo {
 
 __device__ int g_gemm_status_word;
 
-DeviceInfo g_dev[64];
+DeviceInfo g_dev[kMaxDevices];
+DeviceOnce g_dev_once;
 
+// Filled on the first call on a device, under g_dev_once: a second host thread either waits for the table or
+// finds it complete.
 cudaError_t device_info(DeviceInfo **out) {
     int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
+    cudaError_t e = current_device(&dev);
     if (e != cudaSuccess) return e;
-    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-    DeviceInfo &d = g_dev[dev];
-    if (!d.ready) {
-        if ((e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
-        if ((e = cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess) return e;
+    e = g_dev_once.run(dev, [dev]() {
+        DeviceInfo d;
+        cudaError_t e2;
+        if ((e2 = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e2;
+        if ((e2 = cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess) return e2;
         if (d.cc_major == 10) {
             void *p = nullptr;
-            if ((e = cudaGetSymbolAddress(&p, g_gemm_status_word)) != cudaSuccess) return e;
+            if ((e2 = cudaGetSymbolAddress(&p, g_gemm_status_word)) != cudaSuccess) return e2;
             d.status_word = static_cast<int *>(p);
         }
-        d.ready = true;
-    }
-    *out = &d;
+        g_dev[dev] = d;
+        return cudaSuccess;
+    });
+    if (e != cudaSuccess) return e;
+    *out = &g_dev[dev];
     return cudaSuccess;
 }
 
@@ -1252,7 +1353,8 @@ int fill_attrs(cudaLaunchAttribute *attr, unsigned cluster_x, const GemmArgs &g)
 // (1024 x 14336 x k): k = 4096 no gain with any slice count, k = 16384 455 -> 365 us with 8 slices.  So the slice
 // count minimises  tile/s + 3.2 (s - 1) + 4 us  (tile = 0.38 us per k-block) and the split is used only when that
 // is under 0.6 of a tile time.
-void plan_tail(int64_t m, int64_t n, int64_t k, int workers, uint32_t *full_tiles, uint32_t *split, size_t *bytes) {
+void plan_tail(int64_t m, int64_t n, int64_t k, int workers, uint32_t *full_tiles, uint32_t *split, size_t *bytes,
+               double *tail_frac = nullptr) {
     const int64_t tiles = ((m + 255) / 256) * ((n + 255) / 256);
     const int64_t k_blocks = (k + 63) / 64;
     *full_tiles = static_cast<uint32_t>(tiles);
@@ -1278,6 +1380,7 @@ void plan_tail(int64_t m, int64_t n, int64_t k, int workers, uint32_t *full_tile
         if (cost < best) { best = cost; s = c; }
     }
     if (s < 2) return;
+    if (tail_frac) *tail_frac = best / tile_us;        // the split remainder wave, in tile times
     *full_tiles = static_cast<uint32_t>(tiles - rem);
     *split = static_cast<uint32_t>(s);
     const size_t parts = static_cast<size_t>(rem) * (s - 1) * 2;
@@ -1291,13 +1394,10 @@ template <int CTA_GROUP, int BN, int STAGES, int MT, bool BF16>
 cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t stream) {
     using C = Cfg<CTA_GROUP, BN, STAGES, MT>;
     auto kernel = hgemm_tcgen05_kernel<CTA_GROUP, BN, STAGES, MT, BF16>;
-    static bool attr_done[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (!attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    static DeviceOnce smem_once;
+    {
+        const cudaError_t e = allow_dynamic_smem(smem_once, kernel, C::kSmemBytes);
         if (e != cudaSuccess) return e;
-        attr_done[dev] = true;
     }
     CUtensorMap tm_a, tm_b;
     DstMaps tm_c = {};
@@ -1337,16 +1437,16 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(workers * CTA_GROUP), 1, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.blockDim = dim3(MT == 2 ? kThreadsWide : kThreads, 1, 1);
     cfg.dynamicSmemBytes = C::kSmemBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[3];
     cfg.attrs = attr;
     cfg.numAttrs = fill_attrs(attr, CTA_GROUP, g);
-    // Benchmark overrides, read once: PEAKGEMM_TUNE_GROUP_M (raster band height in tiles),
-    // PEAKGEMM_TUNE_FLAGS (the kFlag* switches).
-    static const int env_group_m = getenv("PEAKGEMM_TUNE_GROUP_M") ? atoi(getenv("PEAKGEMM_TUNE_GROUP_M")) : 0;
-    static const int env_flags = getenv("PEAKGEMM_TUNE_FLAGS") ? atoi(getenv("PEAKGEMM_TUNE_FLAGS")) : -1;
+    // Benchmark overrides (builds with PG_ENABLE_TUNING only), read once: PEAKGEMM_TUNE_GROUP_M (raster band
+    // height in tiles), PEAKGEMM_TUNE_FLAGS (the kFlag* switches).
+    static const int env_group_m = tune_env_int("PEAKGEMM_TUNE_GROUP_M", 0);
+    static const int env_flags = tune_env_int("PEAKGEMM_TUNE_FLAGS", -1);
     const uint32_t group_m = env_group_m > 0 ? static_cast<uint32_t>(env_group_m) : 16 / (CTA_GROUP * MT);
     // one tile row (m <= 128): every weight byte is read exactly once, so B streams through L2 (evict first)
     const uint32_t shape_flags = (CTA_GROUP == 1 && g.m <= 128) ? kFlagBEvictFirst : 0u;
@@ -1374,13 +1474,10 @@ template <int BN, int STAGES, bool BF16>
 cudaError_t launch_splitk(const GemmArgs &g, const DeviceInfo &d, int split, cudaStream_t stream) {
     using C = SkCfg<BN, STAGES>;
     auto kernel = hgemm_splitk_kernel<BN, STAGES, BF16>;
-    static bool attr_done[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (!attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    static DeviceOnce smem_once;
+    {
+        const cudaError_t e = allow_dynamic_smem(smem_once, kernel, C::kSmemBytes);
         if (e != cudaSuccess) return e;
-        attr_done[dev] = true;
     }
     CUtensorMap tm_a, tm_b;
     if (!make_tmap(&tm_a, g.a, g.m, g.k, g.lda, kBM, BF16, false) ||
@@ -1405,13 +1502,10 @@ template <int TOK, int STAGES, bool BF16>
 cudaError_t launch_skinny(const GemmArgs &g, const DeviceInfo &d, int split, cudaStream_t stream) {
     using C = SnCfg<TOK, STAGES>;
     auto kernel = hgemm_skinny_kernel<TOK, STAGES, BF16>;
-    static bool attr_done[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (!attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    static DeviceOnce smem_once;
+    {
+        const cudaError_t e = allow_dynamic_smem(smem_once, kernel, C::kSmemBytes);
         if (e != cudaSuccess) return e;
-        attr_done[dev] = true;
     }
     CUtensorMap tm_tok, tm_w;
     if (!make_tmap(&tm_tok, g.a, g.m, g.k, g.lda, TOK, BF16, false) ||
@@ -1468,12 +1562,30 @@ void choose_config(const GemmArgs &g, int sm_count, int *variant, int *block_n) 
             const int64_t tile_m = 128 * v;
             const int64_t tiles = ((g.m + tile_m - 1) / tile_m) * ((g.n + bn - 1) / bn);
             const int64_t workers = sm_count / v;
-            const int64_t waves = (tiles + workers - 1) / workers;
+            double waves = static_cast<double>((tiles + workers - 1) / workers);
+            if (v == 2 && bn == 256 && g.workspace && g.n_extra_dst == 0) {
+                // with a workspace the last partial wave of this configuration is cut into k-slices
+                uint32_t full = 0, split = 0;
+                size_t need = 0;
+                double frac = 1.0;
+                plan_tail(g.m, g.n, g.k, static_cast<int>(workers), &full, &split, &need, &frac);
+                if (split >= 2 && need <= g.workspace_bytes) waves = static_cast<double>(full / workers) + frac;
+            }
             // measured at 8192^3: block_n 128 runs at ~0.72 of block_n 256 per flop (operand traffic per flop doubles)
             const double eff = (bn == 256 ? 1.0 : bn == 128 ? 0.72 : 0.45) * (v == 2 ? 1.06 : 1.0);
-            const double cost = static_cast<double>(waves) * bn / eff;
+            const double cost = waves * bn / eff;
             if (cost < best) { best = cost; best_v = v; best_bn = bn; }
         }
+    }
+    // Two row blocks per CTA pair (512 x 256 tiles): a quarter less operand traffic per flop, measured 1.04-1.06 of
+    // the 256 x 256 pair tile per flop when the waves are full (8192^3, 16384^3, 32768 x 4096 x 16384), but tiles
+    // twice as large quantise worse (4096 x 14336 x 4096: 7 waves of 448 tiles against 13 of 896: 0.87).
+    if (*variant == 0 && (*block_n == 0 || *block_n == 256) && g.m > 256) {
+        const int64_t tiles = ((g.m + 511) / 512) * ((g.n + 255) / 256);
+        const int64_t workers = sm_count / 2;
+        const int64_t waves = (tiles + workers - 1) / workers;
+        const double cost = static_cast<double>(waves) * 512.0 / (1.06 * 1.05);
+        if (cost < best) { best = cost; best_v = 5; best_bn = 256; }
     }
     *variant = best_v;
     *block_n = best_bn;
@@ -1551,19 +1663,13 @@ int hgemm_launch(const GemmArgs &g, int variant, int block_n, int max_sms, cudaS
     if (max_sms > 0 && max_sms < sms) sms = max_sms < 2 ? 2 : max_sms;
     // variant 3 = cluster split-K; chosen automatically when one CTA per tile would leave more than
     // 40 % of the SMs without a tile and k is long enough to split
-    if (g.n_extra_dst > 0 && variant == 0) {      // several destinations: the persistent TMA-store kernels only
-        variant = (g.m > 128) ? 2 : 1;
-        if (block_n == 0) {
-            int v = variant, bn = 0;
-            choose_config(g, sms, &v, &bn);
-            block_n = bn;
-        }
-    }
-    if (g.n_extra_dst > 0 && variant > 2) return kLaunchBadConfig;
+    if (g.n_extra_dst > 0 && variant == 0)        // several destinations: the persistent TMA-store kernels only
+        choose_config(g, sms, &variant, &block_n);
+    if (g.n_extra_dst > 0 && (variant == 3 || variant == 4)) return kLaunchBadConfig;
     if (g.n_extra_dst > 0 && (g.row_scale || g.bias || g.residual)) return kLaunchBadConfig;
-    static const int env_split = getenv("PEAKGEMM_TUNE_SPLITK") ? atoi(getenv("PEAKGEMM_TUNE_SPLITK")) : -1;
+    static const int env_split = tune_env_int("PEAKGEMM_TUNE_SPLITK", -1);
     // variant 4 = skinny kernel (m <= 64, operands swapped); the automatic choice for such m
-    static const bool env_no_skinny = getenv("PEAKGEMM_TUNE_SKINNY") && getenv("PEAKGEMM_TUNE_SKINNY")[0] == '0';
+    static const bool env_no_skinny = tune_env_int("PEAKGEMM_TUNE_SKINNY", 1) == 0;
     if (variant == 4 || (variant == 0 && g.m <= 64 && !env_no_skinny)) {
         if (g.m > 64) return kLaunchBadConfig;
         int sp = choose_skinny_split(g, sms);
@@ -1642,6 +1748,8 @@ size_t hgemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int sm_count) {
     if (split < 2) return 0;
     if (full == 0) return bytes;                      // all remainder: the launch takes the 256-wide pair kernel for it
     GemmArgs g{nullptr, nullptr, nullptr, m, n, k, k, k, n, true};
+    g.workspace = &g;                                 // "a workspace of that size is available": the choice counts on it
+    g.workspace_bytes = bytes;
     int variant = 0, block_n = 0;
     choose_config(g, sm_count, &variant, &block_n);
     return (variant == 2 && block_n == 256) ? bytes : 0;

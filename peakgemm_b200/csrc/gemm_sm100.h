@@ -28,7 +28,8 @@ struct GemmArgs {
 
 enum LaunchResult { kLaunchOk = 0, kLaunchCuda = 1, kLaunchNotSm100 = 2, kLaunchBadConfig = 3 };
 
-// variant: 0 auto, 1 = one CTA per tile, 2 = CTA pair per tile; block_n: 0 auto, 64, 128, 256.
+// variant: 0 auto, 1 = one CTA per tile, 2 = CTA pair per tile, 3 = cluster split-K, 4 = skinny,
+// 5 = CTA pair with two row blocks per CTA (512 x 256 tiles); block_n: 0 auto, 64, 128, 256.
 // max_sms: 0 = all SMs, else an upper bound on the SMs the persistent grid occupies.
 int hgemm_launch(const GemmArgs &g, int variant, int block_n, int max_sms, cudaStream_t stream,
                  cudaError_t *cuda_err);

@@ -112,7 +112,10 @@ extern "C" {
 // Tensor-core probe: runs `iters` k = 64 rounds of 256 x 256 pair MMAs on every SM pair and writes the
 // TFLOP/s reached (2 * 256 * 256 * 64 flop per round and pair).  Synchronises; allocates nothing.
 int pg_probe_tensor_peak(int dtype, int iters, float *tflops_out, float *ms_out) {
-    if ((dtype != PG_F16 && dtype != PG_BF16) || iters < 1 || !tflops_out) return PG_ERR_BAD_ARG;
+    // The kernel's one wait (for its whole MMA chain) is bounded at 4 s; 2^20 rounds take about 0.4 s, so a run
+    // within the cap can never outlast the wait and tear down tensor memory under MMAs still in flight.
+    if ((dtype != PG_F16 && dtype != PG_BF16) || iters < 1 || iters > PG_PROBE_MAX_ITERS || !tflops_out)
+        return PG_ERR_BAD_ARG;
     int dev = 0, sms = 0, cc = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return PG_ERR_CUDA;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

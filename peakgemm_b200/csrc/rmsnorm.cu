@@ -25,6 +25,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "host_util.h"
 #include "rmsnorm.h"
 
 namespace pg {
@@ -268,17 +269,19 @@ rmsnorm_bwd_kernel(uint4 *__restrict__ dx, float *__restrict__ partial, const ui
 // dgamma[c] = sum_p partial[p][c], p in a fixed order.  Block = 32 float4 columns
 // x 32 slices of the partial rows; slices are combined by a shared-memory tree.
 __global__ void __launch_bounds__(1024)
-rmsnorm_dgamma_reduce_kernel(float *__restrict__ dgamma, const float *__restrict__ partial, int nparts, int h4) {
+rmsnorm_dgamma_reduce_kernel(float *__restrict__ dgamma, const float *partial, int nparts, int h4) {
     __shared__ float4 red[32][33];
     // Launched with programmatic stream serialization: this grid may be scheduled while the backward kernel
-    // is still draining; nothing of its output is touched before the dependency has fully completed.
+    // is still draining; nothing of its output is touched before the dependency has fully completed.  `partial`
+    // is written by that kernel AFTER this grid may have started, so it is not read-only for this grid's
+    // lifetime: plain L2 loads (ld.global.cg), never the read-only path.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int cx = threadIdx.x & 31, sl = threadIdx.x >> 5;
     const int col = blockIdx.x * 32 + cx;
     float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
     if (col < h4) {
         for (int p = sl; p < nparts; p += 32) {
-            const float4 v = __ldg(reinterpret_cast<const float4 *>(partial) + static_cast<int64_t>(p) * h4 + col);
+            const float4 v = __ldcg(reinterpret_cast<const float4 *>(partial) + static_cast<int64_t>(p) * h4 + col);
             a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
         }
     }
@@ -347,20 +350,7 @@ cudaError_t bwd_launch(const RmsBwdArgs &a, int grid, cudaStream_t stream) {
      : (plan).vpt == 2        ? FN<1024, 2, 1>(__VA_ARGS__)                         \
                               : FN<1024, 8, 1>(__VA_ARGS__))
 
-int g_sm_count[64] = {};
-
-cudaError_t sm_count(int *out) {
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return e;
-    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-    if (g_sm_count[dev] == 0) {
-        e = cudaDeviceGetAttribute(&g_sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
-        if (e != cudaSuccess) return e;
-    }
-    *out = g_sm_count[dev];
-    return cudaSuccess;
-}
+cudaError_t sm_count(int *out) { return current_device_sm_count(out); }
 
 }  // namespace
 

@@ -17,6 +17,7 @@
 #include <stdint.h>
 
 #include "ptx.cuh"
+#include "host_util.h"
 #include "rmsnorm.h"
 
 namespace pg {
@@ -67,18 +68,11 @@ rmsnorm_rstd_kernel(float *__restrict__ rstd, const uint4 *__restrict__ x, int64
 
 cudaError_t rmsnorm_rstd_launch(float *rstd, const void *x, int64_t rows, int64_t h, float eps, bool bf16,
                                 cudaStream_t stream) {
-    static int sm_count[64] = {};
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
+    int sms = 0;
+    const cudaError_t e = current_device_sm_count(&sms);
     if (e != cudaSuccess) return e;
-    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-    if (sm_count[dev] == 0) {
-        int n = 0;
-        if ((e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
-        sm_count[dev] = n;
-    }
     const int64_t want = (rows + kWarpsPerCta - 1) / kWarpsPerCta;
-    const int64_t cap = static_cast<int64_t>(sm_count[dev]) * 8;      // 64 warps per SM
+    const int64_t cap = static_cast<int64_t>(sms) * 8;      // 64 warps per SM
     const unsigned grid = static_cast<unsigned>(want < cap ? want : cap);
     const uint32_t vecs = static_cast<uint32_t>(h / 8);
     const float inv_h = 1.0f / static_cast<float>(h);

@@ -26,6 +26,7 @@
 #include <stdint.h>
 #include <stdlib.h>
 
+#include "host_util.h"
 #include "ptx.cuh"
 #include "rmsnorm.h"
 
@@ -72,7 +73,7 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, const Wa
             if (t0 == 0) t0 = now;
             else if (now - t0 > kWaitTimeoutNs) {
                 *ctx.abort_flag = 1;
-                atomicCAS(ctx.status, 0, code);
+                if (ctx.status) atomicCAS(ctx.status, 0, code);
                 return false;
             }
         }
@@ -407,8 +408,9 @@ Plan make_plan(int64_t h, bool bwd) {
     int T = static_cast<int>((h8 / per_thread + 31) / 32 * 32);
     if (T < 32) T = 32;
     if (T > 256) T = 256;
-    // Benchmark override, read once: PEAKGEMM_TUNE_RMS_T = threads per consumer group (32..256).
-    static const int env_t = getenv("PEAKGEMM_TUNE_RMS_T") ? atoi(getenv("PEAKGEMM_TUNE_RMS_T")) : 0;
+    // Benchmark override (builds with PG_ENABLE_TUNING only), read once: PEAKGEMM_TUNE_RMS_T = threads per
+    // consumer group (32..256).
+    static const int env_t = tune_env_int("PEAKGEMM_TUNE_RMS_T", 0);
     if (env_t >= 32 && env_t <= 256 && env_t % 32 == 0 && (h8 + env_t - 1) / env_t <= 8) T = env_t;
     const int need = static_cast<int>((h8 + T - 1) / T);
     p.vpt = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
@@ -436,20 +438,28 @@ Plan make_plan(int64_t h, bool bwd) {
     return p;
 }
 
-int g_sms[64] = {};
-int *g_status_ptr[64] = {};
+int g_sms[kMaxDevices] = {};
+int *g_status_ptr[kMaxDevices] = {};
+DeviceOnce g_setup_once;
 
+// SM count and the address of the status word, looked up on the first call on a device.  Both tables are
+// filled under g_setup_once before its ready flag is published, so no thread can see the SM count without
+// the status pointer.
 cudaError_t device_setup(int *sms, int **status) {
     int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
+    cudaError_t e = current_device(&dev);
     if (e != cudaSuccess) return e;
-    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-    if (g_sms[dev] == 0) {
-        if ((e = cudaDeviceGetAttribute(&g_sms[dev], cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+    e = g_setup_once.run(dev, [dev]() {
+        int n = 0;
         void *p = nullptr;
-        if ((e = cudaGetSymbolAddress(&p, g_rms_status_word)) != cudaSuccess) return e;
+        cudaError_t e2;
+        if ((e2 = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e2;
+        if ((e2 = cudaGetSymbolAddress(&p, g_rms_status_word)) != cudaSuccess) return e2;
         g_status_ptr[dev] = static_cast<int *>(p);
-    }
+        g_sms[dev] = n;
+        return cudaSuccess;
+    });
+    if (e != cudaSuccess) return e;
     *sms = g_sms[dev];
     *status = g_status_ptr[dev];
     return cudaSuccess;
@@ -460,13 +470,10 @@ cudaError_t launch_one(void *out, float *partial, const void *x, const void *dy,
                        int64_t rows, int64_t h, float eps, const Plan &p, int grid, int *status,
                        cudaStream_t stream) {
     auto kernel = rms_staged_kernel<BWD, VPT, BF16, INCR>;
-    static bool attr_done[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (!attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    static DeviceOnce smem_once;
+    {
+        const cudaError_t e = allow_dynamic_smem(smem_once, kernel, static_cast<int>(kSmemBudget));
         if (e != cudaSuccess) return e;
-        attr_done[dev] = true;
     }
     kernel<<<grid, Threads<BWD, VPT>::kTotal, p.smem, stream>>>(static_cast<uint4 *>(out), partial, static_cast<const uint4 *>(x),
                                                static_cast<const uint4 *>(dy), gamma, rows,
@@ -498,8 +505,9 @@ cudaError_t launch_any(void *out, float *partial, const void *x, const void *dy,
 }  // namespace
 
 bool rmsnorm_staged_supported(int64_t h, bool bwd) {
-    // Benchmark override, read once: PEAKGEMM_TUNE_RMS_STAGED=0 falls back to the register-resident kernels.
-    static const bool disabled = getenv("PEAKGEMM_TUNE_RMS_STAGED") && getenv("PEAKGEMM_TUNE_RMS_STAGED")[0] == '0';
+    // Benchmark override (builds with PG_ENABLE_TUNING only), read once: PEAKGEMM_TUNE_RMS_STAGED=0 falls back to
+    // the register-resident kernels.
+    static const bool disabled = tune_env_int("PEAKGEMM_TUNE_RMS_STAGED", 1) == 0;
     if (disabled) return false;
     return make_plan(h, bwd).ok;
 }

@@ -19,6 +19,7 @@
 #include <stdint.h>
 
 #include "../../include/peakgemm.h"
+#include "host_util.h"
 #include "rmsnorm.h"
 
 namespace {
@@ -64,10 +65,7 @@ extern "C" int pg_rmsnorm_bwd_static(void *dx, float *dgamma, const void *dy, co
     }
     float *scratch = nullptr;
     const cudaError_t e = scratch_address(&scratch);
-    if (e != cudaSuccess) {
-        cudaGetLastError();
-        return PG_ERR_CUDA;
-    }
+    if (e != cudaSuccess) return pg::record_cuda_failure(e);      // pg_last_cuda_error() then names the failed call
     // Same kernels, same order of operations as pg_rmsnorm_bwd: the results are bit-identical.
     return pg_rmsnorm_bwd(dx, dgamma, dy, x, gamma, rows, h, eps, dtype, scratch, PG_STATIC_SCRATCH_BYTES, stream);
 }

@@ -101,8 +101,13 @@ def test_argument_checks_return_before_any_cuda_call():
 def test_config_choice_is_host_arithmetic():
     from peakgemm_b200 import capi
 
-    assert capi.hgemm_config(8192, 8192, 8192) == (2, 256)        # headline shape: CTA pairs, 256-wide tiles
-    assert capi.hgemm_config(16384, 16384, 16384) == (2, 256)
+    assert capi.hgemm_config(8192, 8192, 8192) == (5, 256)        # headline shape: CTA pairs, 512 x 256 tiles
+    assert capi.hgemm_config(16384, 16384, 16384) == (5, 256)
+    assert capi.hgemm_config(32768, 4096, 16384) == (5, 256)      # one rank's block of the sharded benchmark shape
+    assert capi.hgemm_config(2048, 2048, 2048) == (2, 256)        # 32 large tiles would idle most SM pairs
+    assert capi.hgemm_config(4096, 14336, 4096) == (2, 256)       # 448 large tiles: 7 waves for 6.05 waves of work
+    assert capi.hgemm_config(4096, 4096, 256) == (5, 256)         # the shapes tests/test_fused_gpu.py relies on
+    assert capi.hgemm_config(4000, 4104, 136) == (5, 256)
     v, bn = capi.hgemm_config(16, 4096, 4096)
     assert v == 1 and bn == 64                                    # one tile row: no pair, most CTAs
     v, bn = capi.hgemm_config(128, 128256, 4096)
@@ -110,8 +115,8 @@ def test_config_choice_is_host_arithmetic():
     for m in (1, 100, 129, 1000, 5000):
         for n in (8, 512, 4096, 14336):
             v, bn = capi.hgemm_config(m, n, 4096)
-            assert v in (1, 2) and bn in (64, 128, 256)
-            assert not (v == 2 and m <= 128)
+            assert v in (1, 2, 5) and bn in (64, 128, 256)
+            assert not (v in (2, 5) and m <= 128)
     assert capi.lib().pg_hgemm_config(0, 8, 8, 148, None, None) == 1
 
 
