@@ -41,6 +41,14 @@ METRIC = "hgemm_bf16_tflops_8192"
 UNIT = "TFLOP/s"
 
 
+def bench_config(world: int) -> dict:
+    """The `config` object of the JSON line; both arms (ours, --impl reference) print the same one."""
+    w = WORKLOAD if world == 1 else WORKLOAD + (f"; x{world} ranks, rank r owns column block r of "
+                                                f"B[{N * world},{K}] (A replicated), no gather")
+    return {"workload": w, "l2": f"inputs+output {2 * (M * K + N * K + M * N) / 1e6:.0f} MB per step vs 126 MB L2: "
+                                 "larger than L2, no flush between iterations"}
+
+
 def measured_peaks() -> dict:
     path = os.path.join(REPO, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -176,8 +184,9 @@ def run_reference_arm(args) -> None:
         "impl": "reference", "metric": METRIC, "value": tflops, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "note": "the reference has no CPU implementation; this is its oracle "
-                   "formula (src/impl/sgemm_impl.h:17-25) as an fp32 CPU matmul on a bounded row band"},
+        "config": bench_config(int(os.environ.get("WORLD_SIZE", "1"))),
+        "note": "the reference has no CPU implementation; this is its oracle formula (src/impl/sgemm_impl.h:17-25) "
+                "as an fp32 CPU matmul on a bounded row band",
         "cpu_baseline": cb,
         "e2e": {"value": tflops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -383,6 +392,236 @@ def chain_sweep() -> list:
     return rows
 
 
+def e2e_ms(a, b, c, steps: int):
+    """ms per step of PeakGemm.gemm_peak with HOST buffers: every step copies ITS inputs host -> device from pinned
+    memory, runs the operator and reads ITS result back.  Three buffer sets and three streams (copy-in, operator,
+    copy-out) let step i+1's upload and step i-1's download overlap step i's GEMM: PCIe is full duplex, the link is
+    the bottleneck, not the kernel."""
+    import torch
+
+    import PeakGemm
+
+    ah, bh = a.cpu().pin_memory(), b.cpu().pin_memory()
+    ch = torch.empty(c.shape, dtype=c.dtype).pin_memory()
+    nb = 3
+    ad = [torch.empty_like(a) for _ in range(nb)]
+    bd = [torch.empty_like(b) for _ in range(nb)]
+    cd = [torch.empty_like(c) for _ in range(nb)]
+    s_in, s_op, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    ev_in = [torch.cuda.Event() for _ in range(nb)]
+    ev_op = [torch.cuda.Event() for _ in range(nb)]
+    ev_out = [torch.cuda.Event() for _ in range(nb)]
+
+    def run(n_steps):
+        main = torch.cuda.current_stream()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        t0.record(main)
+        for st in (s_in, s_op, s_out):
+            st.wait_event(t0)
+        for s_ in range(n_steps):
+            i = s_ % nb
+            with torch.cuda.stream(s_in):
+                if s_ >= nb:
+                    s_in.wait_event(ev_op[i])          # the GEMM that read this buffer set has finished
+                ad[i].copy_(ah, non_blocking=True)
+                bd[i].copy_(bh, non_blocking=True)
+                ev_in[i].record(s_in)
+            with torch.cuda.stream(s_op):
+                s_op.wait_event(ev_in[i])
+                if s_ >= nb:
+                    s_op.wait_event(ev_out[i])         # the previous result in this set has been read back
+                PeakGemm.gemm_peak(cd[i], ad[i], bd[i])
+                ev_op[i].record(s_op)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_op[i])
+                ch.copy_(cd[i], non_blocking=True)
+                ev_out[i].record(s_out)
+        for st in (s_in, s_op, s_out):
+            main.wait_stream(st)
+        t1.record(main)
+        torch.cuda.synchronize()
+        return t0.elapsed_time(t1) / n_steps
+
+    e2e_steps = max(6, min(steps, 12))
+    run(3)
+    return run(e2e_steps), e2e_steps
+
+
+def reference_style_timing(a, b, c, flops: float) -> dict:
+    """The two ways the reference times its kernel, applied to ours on the same inputs:
+    a single launch between two events right after a device synchronisation, nothing warm beyond the module itself
+    (test/cpp/test_gemm_half.cpp:109-129; median and best of 5 such launches, an L2 flush before each), and the
+    average self-CUDA time torch.profiler attributes to the kernel over 40 calls after 10 warm-ups
+    (test/test_gemm.py:69-96)."""
+    import torch
+
+    from peakgemm_b200 import capi
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    cold = []
+    for _ in range(5):
+        flush.zero_()                       # 256 MB written: nothing of A, B or C is left in the 126 MB L2
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        capi.hgemm(c, a, b)
+        e1.record()
+        torch.cuda.synchronize()
+        cold.append(e0.elapsed_time(e1))
+    out = {"single_cold_launch_ms_median": statistics.median(cold), "single_cold_launch_ms_best": min(cold),
+           "single_cold_launch_tflops_median": flops / (statistics.median(cold) * 1e-3) / 1e12}
+    try:
+        from torch.profiler import ProfilerActivity, profile
+
+        for _ in range(10):
+            capi.hgemm(c, a, b)
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(40):
+                capi.hgemm(c, a, b)
+            torch.cuda.synchronize()
+        rows = [e for e in prof.key_averages() if "hgemm" in e.key]
+        if rows:
+            us = max(rows, key=lambda e: e.self_device_time_total).self_device_time_total / 40.0
+            out["profiler_self_cuda_ms_avg_of_40"] = us / 1e3
+            out["profiler_tflops"] = flops / (us * 1e-6) / 1e12
+    except Exception as exc:  # noqa: BLE001  (the profiler needs CUPTI; report rather than fail the bench)
+        out["profiler_unavailable"] = repr(exc)[:200]
+    return out
+
+
+def config5_block(world: int, rank: int, steps: int = 3) -> dict:
+    """benchmark config 5 on the ranks of this run, as part of the default JSON line: m = n = 32768, k = 16384 bf16,
+    B column-sharded over the ranks with A replicated (STRONG scaling: the problem is fixed, N = 1 is the
+    denominator).  Timed without a gather, with the NCCL all-gather (native shard-major result, and copied to
+    row-major) and with the gather fused into the GEMM epilogue (row-major on every rank, peer stores).  CUDA events,
+    max over ranks.  `parity`: 16 sampled rows of this rank's block against an fp32 product of the same inputs
+    (acceptance bound), and at N > 1 the fused result against the NCCL result bit for bit."""
+    import math
+
+    import torch
+    import torch.distributed as dist
+
+    from peakgemm_b200 import capi
+    from peakgemm_b200.dist import PeerMatrix, ShardedGemm
+
+    m = n = 32768
+    k = 16384
+    sg = ShardedGemm(n)
+    g = torch.Generator(device="cuda").manual_seed(4)
+    a = (torch.rand(m, k, device="cuda", generator=g) * 2 - 1).to(torch.bfloat16)
+    g.manual_seed(400 + rank)
+    b = (torch.rand(sg.n_local, k, device="cuda", generator=g) * 2 - 1).to(torch.bfloat16)
+    out = torch.empty(m, sg.n_local, dtype=torch.bfloat16, device="cuda")
+
+    def timed(fn, reps):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / reps], device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    flop = 2.0 * m * n * k
+    res = {"workload": "bf16 GEMM m=n=32768 k=16384, B column-sharded over the ranks, A replicated (benchmark "
+                       "configs[4]); strong scaling", "n_gpus": world, "steps": steps, "flop": flop}
+    res["no_gather_ms"] = timed(lambda: sg.local(a, b, out=out), steps)
+    res["tflops"] = flop / (res["no_gather_ms"] * 1e-3) / 1e12
+    # parity of this rank's block on sampled rows
+    rows = (torch.arange(16, device="cuda") * (m // 16) + 5)
+    ref = a[rows].float() @ b.float().t()
+    tol = (2e-2 * math.sqrt(k / 4096.0) + 2.0 ** -8) * ref.abs().max().item()
+    ok = torch.tensor([int((out[rows].float() - ref).abs().max().item() <= tol)], device="cuda")
+    del ref
+    if world == 1:
+        full_b = b
+        t_cublas = timed(lambda: torch.matmul(a, full_b.t(), out=out), steps)
+        res["cublas_ms"] = t_cublas
+        res["cublas_tflops"] = flop / (t_cublas * 1e-3) / 1e12
+    else:
+        res["nccl_gather_shard_major_ms"] = timed(
+            lambda: sg.gathered(a, b, layout="shard_major", bands=4, max_sms=140), steps)
+        res["nccl_gather_ms"] = timed(lambda: sg.gathered(a, b, layout="row_major", bands=4, max_sms=140), steps)
+        pm = PeerMatrix(m, n, torch.bfloat16)
+        res["fused_gather_ms"] = timed(lambda: sg.gathered_fused(pm, a, b), steps)
+        nccl = sg.gathered(a, b, layout="row_major", bands=4, max_sms=140)
+        fused = sg.gathered_fused(pm, a, b)
+        torch.cuda.synchronize()
+        same = torch.equal(fused, nccl)
+        ok = ok * int(same)
+        del nccl, fused
+        pm.close()
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        res["gather_bytes_received_per_gpu"] = 2 * m * (n - sg.n_local)
+    res["parity"] = bool(ok.item())
+    res["device_status"] = capi.device_status()
+    del a, b, out
+    torch.cuda.empty_cache()
+    return res
+
+
+def rmsnorm_sharded_block(world: int, rank: int, peaks: dict, steps: int = 10) -> dict:
+    """benchmark config 4 ([32768, H] bf16, H = 4096 and 8192) with the rows sharded over the ranks of this run
+    (strong scaling): forward, backward with the local dgamma only, and backward with the global dgamma
+    (all-gather of the partial vectors, summed in rank order).  Aggregate GB/s = algorithmic bytes of the WHOLE
+    problem (4RH + 4H, 6RH + 8H) / max-over-ranks time."""
+    import torch
+    import torch.distributed as dist
+
+    from peakgemm_b200.dist import ShardedRmsNorm
+
+    R = 32768
+    out = {"n_gpus": world, "rows_total": R}
+    for H in (4096, 8192):
+        sn = ShardedRmsNorm(R)
+        g = torch.Generator(device="cuda").manual_seed(3 + 10 * rank)
+        x = torch.randn(sn.rows_local, H, device="cuda", generator=g).to(torch.bfloat16)
+        dy = torch.randn(sn.rows_local, H, device="cuda", generator=g).to(torch.bfloat16)
+        gamma = (1 + 0.1 * torch.randn(H, device="cuda", generator=torch.Generator(device="cuda").manual_seed(3))).float()
+        y = torch.empty_like(x)
+
+        def timed(fn):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / steps], device="cuda")
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return t.item()
+
+        t_f = timed(lambda: sn.forward(x, gamma, out=y))
+        t_b = timed(lambda: sn.backward(dy, x, gamma, reduce="none"))
+        t_bg = timed(lambda: sn.backward(dy, x, gamma, reduce="ordered"))
+        bf, bb = 4 * R * H + 4 * H, 6 * R * H + 8 * H
+        out[f"h{H}"] = {"fwd_ms": t_f, "fwd_gbs": bf / t_f / 1e6, "bwd_local_dgamma_ms": t_b,
+                        "bwd_local_dgamma_gbs": bb / t_b / 1e6, "bwd_global_dgamma_ms": t_bg,
+                        "bwd_global_dgamma_gbs": bb / t_bg / 1e6,
+                        "fwd_frac_of_measured_hbm_per_gpu": bf / t_f / 1e6 / world / peaks["hbm_gbs"],
+                        "bwd_frac_of_measured_hbm_per_gpu": bb / t_b / 1e6 / world / peaks["hbm_gbs"]}
+        del x, dy, y
+    return out
+
+
 def config5(args) -> None:
     """benchmark config 5: m = n = 32768, k = 16384 bf16, B column-sharded over the ranks (strong scaling),
     timed without a gather, with the all-gather (native shard-major result) and with the copy to row-major."""
@@ -565,10 +804,8 @@ def main() -> None:
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD if world == 1 else WORKLOAD + f"; x{world} ranks, rank r owns column block r "
-                   f"of B[{N * world},{K}] (A replicated), no gather",
-                   "l2": f"inputs+output {6 * M * N / 1e6:.0f} MB per step vs 126 MB L2",
-                   "kernel": f"variant={args.variant} block_n={args.block_n} (0 = automatic)"},
+        "config": bench_config(world),
+        "kernel": f"variant={args.variant} block_n={args.block_n} (0 = automatic)",
         "gpu_launches": args.steps,
         "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks[peak_key], "unit": "TFLOP/s",
                      "frac": per_gpu / peaks[peak_key],
@@ -577,65 +814,23 @@ def main() -> None:
                      "traffic": ncu_traffic("hgemm_tcgen05_kernel_8192")},
     }
 
-    if rank == 0 and not args.no_extras and world == 1:
-        # ---- end to end through the torch operator with host buffers
-        import PeakGemm
-
-        ah, bh = a.cpu().pin_memory(), b.cpu().pin_memory()
-        ch = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
-        # Every step copies ITS inputs host -> device, runs the operator and reads ITS result back.  Three
-        # buffer sets and three streams (copy-in, operator, copy-out) let step i+1's upload and step i-1's
-        # download overlap step i's GEMM: PCIe is full duplex, the link is the bottleneck, not the kernel.
-        nb = 3
-        ad = [torch.empty_like(a) for _ in range(nb)]
-        bd = [torch.empty_like(b) for _ in range(nb)]
-        cd = [torch.empty_like(c) for _ in range(nb)]
-        s_in, s_op, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
-        ev_in = [torch.cuda.Event() for _ in range(nb)]
-        ev_op = [torch.cuda.Event() for _ in range(nb)]
-        ev_out = [torch.cuda.Event() for _ in range(nb)]
-
-        def e2e_run(steps):
-            main = torch.cuda.current_stream()
-            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            torch.cuda.synchronize()
-            t0.record(main)
-            for st in (s_in, s_op, s_out):
-                st.wait_event(t0)
-            for s_ in range(steps):
-                i = s_ % nb
-                with torch.cuda.stream(s_in):
-                    if s_ >= nb:
-                        s_in.wait_event(ev_op[i])          # the GEMM that read this buffer set has finished
-                    ad[i].copy_(ah, non_blocking=True)
-                    bd[i].copy_(bh, non_blocking=True)
-                    ev_in[i].record(s_in)
-                with torch.cuda.stream(s_op):
-                    s_op.wait_event(ev_in[i])
-                    if s_ >= nb:
-                        s_op.wait_event(ev_out[i])         # the previous result in this set has been read back
-                    PeakGemm.gemm_peak(cd[i], ad[i], bd[i])
-                    ev_op[i].record(s_op)
-                with torch.cuda.stream(s_out):
-                    s_out.wait_event(ev_op[i])
-                    ch.copy_(cd[i], non_blocking=True)
-                    ev_out[i].record(s_out)
-            for st in (s_in, s_op, s_out):
-                main.wait_stream(st)
-            t1.record(main)
-            torch.cuda.synchronize()
-            return t0.elapsed_time(t1) / steps
-
-        e2e_steps = max(6, min(args.steps, 12))
-        e2e_run(3)
-        t_e2e = e2e_run(e2e_steps)
-        line["e2e"] = {"value": flops_step / (t_e2e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": t_e2e,
-                       "steps": e2e_steps, "h2d_bytes_per_step": 2 * (M * K + N * K),
-                       "d2h_bytes_per_step": 2 * M * N,
+    if not args.no_extras:
+        # ---- end to end through the torch operator with host buffers: every rank, max over ranks
+        t_e2e, e2e_steps = e2e_ms(a, b, c, args.steps)
+        t = torch.tensor([t_e2e], device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        t_e2e = t.item()
+        line["e2e"] = {"value": world * flops_step / (t_e2e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": t_e2e,
+                       "steps": e2e_steps, "h2d_bytes_per_step": world * 2 * (M * K + N * K),
+                       "d2h_bytes_per_step": world * 2 * M * N,
                        "how": "PeakGemm.gemm_peak on pinned-host inputs: H2D of A and B, the operator, D2H of C every "
-                              "step; 3 buffer sets on 3 streams so consecutive steps overlap on the full-duplex link",
-                       "pcie_in_gbs": 2 * (M * K + N * K) / (t_e2e * 1e-3) / 1e9}
-        del ah, bh, ch, ad, bd, cd
+                              "step on every rank; 3 buffer sets on 3 streams so consecutive steps overlap on the "
+                              "full-duplex link; max over ranks",
+                       "pcie_in_gbs_per_gpu": 2 * (M * K + N * K) / (t_e2e * 1e-3) / 1e9}
+    if rank == 0 and not args.no_extras and world == 1:
+        # ---- the reference's own timing styles next to the steady-state figure
+        line["reference_style_timing"] = reference_style_timing(a, b, c, flops_step)
         # ---- comparators on the same GPU and inputs (never on the product path)
         t_cublas = time_cuda(lambda: torch.matmul(a, b.t(), out=c), args.steps, args.warmup)
         line["cublas"] = {"tflops": flops_step / (t_cublas * 1e-3) / 1e12, "ms": t_cublas}
@@ -650,11 +845,15 @@ def main() -> None:
                                                     "what": "reference mma.sync hgemm_peak compiled for sm_100a"}
         line["rmsnorm"] = rmsnorm_numbers(peaks, args.steps, args.warmup)
         line["cpu_baseline"] = cpu_gemm_baseline()
-    elif rank == 0 and world > 1:
-        line["e2e"] = None
     if args.no_extras and args.cublas and world == 1:
         t_cublas = time_cuda(lambda: torch.matmul(a, b.t(), out=c), args.steps, args.warmup)
         line["cublas"] = {"tflops": flops_step / (t_cublas * 1e-3) / 1e12, "ms": t_cublas}
+    if not args.no_extras and args.size == 8192 and not args.shape:
+        # ---- the multi-GPU split of the sharded benchmark shape on the same ranks (N = 1: its denominator)
+        del a, b, c
+        torch.cuda.empty_cache()
+        line["config5"] = config5_block(world, rank)
+        line["rmsnorm_sharded"] = rmsnorm_sharded_block(world, rank, peaks)
     line["clocks"] = clocks.summary()
 
     if rank == 0:

@@ -22,7 +22,9 @@ REF_OUT = os.path.join(HERE, "_ref")
 CPU_LIB = os.path.join(BUILD, "liboracle.so")
 DEV_LIB = os.path.join(BUILD, "liboracle_device.so")
 REF_LIB = os.path.join(REF_OUT, "libref_peakgemm.so")
-DEFAULT_REFERENCE = os.environ.get("PEAKGEMM_REFERENCE_DIR", "/root/reference")
+# A checkout of the reference project: PEAKGEMM_REFERENCE_DIR, else a directory named "reference" beside this
+# repository.  Absent: the reference library is simply not built.
+DEFAULT_REFERENCE = os.environ.get("PEAKGEMM_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
 def _nvcc() -> str:

@@ -30,6 +30,9 @@ INCLUDE = os.path.join(REPO_DIR, "include")
 
 DEVICE_LIB = os.path.join(PKG_DIR, "libPeakGemm_device.so")
 TORCH_LIB = os.path.join(PKG_DIR, "libPeakGemm.so")
+# The same device library compiled with -DPG_TEST_SHORT_WAIT: bounded waits of 2 ms and a switch that makes one
+# signal go missing.  Loaded only by tests/test_wait_timeout_gpu.py; nothing in the package opens it.
+WAITTEST_LIB = os.path.join(PKG_DIR, "libPeakGemm_device_waittest.so")
 
 DEVICE_SOURCES = ["gemm_sm100.cu", "rmsnorm.cu", "rmsnorm_staged.cu", "rmsnorm_static.cu", "rmsnorm_rstd.cu", "peer.cu", "sgemm.cu", "probes.cu", "api.cu"]
 DEVICE_HEADERS = ["ptx.cuh", "gemm_sm100.h", "host_util.h", "rmsnorm.h", "sgemm.h", os.path.join(INCLUDE, "peakgemm.h")]
@@ -93,6 +96,29 @@ def build_device_lib(force: bool = False, verbose: bool = False, tuning: bool = 
     return DEVICE_LIB
 
 
+def build_waittest_lib(force: bool = False, verbose: bool = False) -> str:
+    srcs = [os.path.join(CSRC, s) for s in DEVICE_SOURCES]
+    hdrs = [h if os.path.isabs(h) else os.path.join(CSRC, h) for h in DEVICE_HEADERS]
+    if not force and _newer(WAITTEST_LIB, srcs + hdrs):
+        return WAITTEST_LIB
+    obj_dir = os.path.join(PKG_DIR, "build", "waittest")
+    os.makedirs(obj_dir, exist_ok=True)
+    objs, procs = [], []
+    for s in srcs:
+        o = os.path.join(obj_dir, os.path.basename(s) + ".o")
+        objs.append(o)
+        cmd = [_nvcc(), *NVCC_FLAGS, "-DPG_TEST_SHORT_WAIT", "-I", INCLUDE, "-c", s, "-o", o]
+        if verbose:
+            print("+", " ".join(cmd), flush=True)
+        procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    for cmd, p in procs:
+        out, _ = p.communicate()
+        if p.returncode != 0:
+            raise RuntimeError(f"nvcc failed: {' '.join(cmd)}\n{out}")
+    _run([_nvcc(), "-shared", "-o", WAITTEST_LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a"], verbose)
+    return WAITTEST_LIB
+
+
 def build_torch_lib(force: bool = False, verbose: bool = False) -> str:
     src = os.path.join(CSRC, "torch_shim.cpp")
     if not force and _newer(TORCH_LIB, [src, os.path.join(INCLUDE, "peakgemm.h"), DEVICE_LIB]):
@@ -116,7 +142,9 @@ def build_torch_lib(force: bool = False, verbose: bool = False) -> str:
 
 
 def build_all(force: bool = False, verbose: bool = False, tuning: bool = False) -> tuple[str, str]:
-    return build_device_lib(force or tuning, verbose, tuning), build_torch_lib(force, verbose)
+    libs = build_device_lib(force or tuning, verbose, tuning), build_torch_lib(force, verbose)
+    build_waittest_lib(force, verbose)
+    return libs
 
 
 if __name__ == "__main__":

@@ -56,7 +56,11 @@
 //   * fused epilogue terms  out = row_scale[row] * acc + bias[col] + residual[row, col]  (EpiArgs);
 //   * several destinations for the output tile (DstMaps): the column-sharded caller's gather over NVLink;
 //   * tail split (TailArgs): the last partial wave of tiles cut into k-slices over the idle workers, partial
-//     sums through a caller workspace, launched cooperatively.
+//     sums through a caller workspace, launched cooperatively;
+//   * producer synchronisation (TailArgs::wave_sync, large problems): the producers of all workers meet at the first
+//     and every 8th k-block of a tile through one global counter, so that workers sharing an A or B panel fetch the
+//     same k-block at nearly the same time (L2 hits and merged requests instead of repeated DRAM reads).  A wait
+//     there has a short patience and no consequence for the result, so it needs no cooperative launch.
 // The file also holds the two kernels for few output tiles (cluster split-K, swapped-operand skinny), which
 // share the fused epilogue terms, and the host side: tensor-map cache, configuration choice, launches.
 
@@ -88,7 +92,17 @@ constexpr uint32_t kThreadsWide = 64 + 32 * kEpiWarpsWide;
 constexpr uint32_t kStoreCols = 64;     // columns per TMA store box (128 bytes)
 constexpr uint32_t kStoreRows = 32;     // rows per TMA store box (one warp's lanes)
 constexpr uint32_t kStageBufBytes = kStoreRows * kStoreCols * 2;  // 4096
+#ifdef PG_TEST_SHORT_WAIT
+// Test build (libPeakGemm_device_waittest.so, never shipped as the product): waits give up after 2 ms, and a
+// switch in device memory makes ONE signal go missing, so that the give-up path itself can be exercised: the
+// waiting role records its code, the CTA drains, the kernel returns and the context stays usable.  The missing
+// signal is chosen so that nothing is in flight when the roles drain: the MMAs have completed, only the
+// "accumulator ready" commit is withheld, so the epilogue warps are the ones that give up.
+constexpr uint64_t kWaitTimeoutNs = 2000000ull;
+__device__ int g_test_withhold_acc_commit;
+#else
 constexpr uint64_t kWaitTimeoutNs = 2000000000ull;                // 2 s
+#endif
 // Default switches.  ncu sweep at 8192^3 (pair kernel, band height 8): serpentine + A evict-last reads 943 MB
 // from DRAM against 1051 MB with no hints; an evict-first hint on B costs +60 %.
 constexpr uint32_t kDefaultFlags = 4u | 32u;
@@ -261,6 +275,9 @@ struct TailArgs {
     uint32_t split;
     float *ws;
     uint32_t *flags;
+    uint32_t *wave_sync;    // null, or a zeroed counter: the producers keep the workers within one tile of each other
+    uint32_t sync_kb;       // k-blocks between two synchronisation points inside a tile (0: only at the tile's start)
+    uint32_t sync_lag;      // the wait for a point comes this many k-blocks after the arrival at it
 };
 
 struct Unit {
@@ -300,6 +317,15 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p) {
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+// Counter of a pure timing barrier: no data is published through it, so neither side needs a fence.
+__device__ __forceinline__ void red_relaxed_gpu_add(uint32_t *p, uint32_t v) {
+    asm volatile("red.relaxed.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_relaxed_gpu(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ void st_release_gpu(uint32_t *p, uint32_t v) {
     asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -318,6 +344,25 @@ __device__ __forceinline__ bool wait_flag(const uint32_t *flag, const WaitCtx &c
                 if (ctx.status) atomicCAS(ctx.status, 0, static_cast<int>(kStEpiTailFlag));
                 return false;
             }
+        }
+    }
+    return true;
+}
+
+// Waits until the counter has reached `target` (wrap-safe), for at most kSyncPatienceNs.  The counter only keeps
+// workers in step, nothing is published through it, so running out of patience is not an error: the caller stops
+// waiting at further points (it keeps announcing its own arrivals) and the kernel's results are the same.  This is
+// also what makes the scheme safe without a cooperative launch: if part of the grid is not resident yet (another
+// kernel holds some SMs), the resident workers lose one patience interval and then run unsynchronised.
+constexpr uint64_t kSyncPatienceNs = 50000ull;
+__device__ __forceinline__ bool wait_count_patiently(const uint32_t *counter, uint32_t target) {
+    uint64_t t0 = 0;
+    uint32_t spins = 0;
+    while (static_cast<int32_t>(ld_relaxed_gpu(counter) - target) < 0) {
+        if ((++spins & 15u) == 0) {
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kSyncPatienceNs) return false;
         }
     }
     return true;
@@ -397,8 +442,8 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
             // In a pair, both CTAs' loads complete on the LEADER's full[s].
             const uint32_t full0 = (CTA_GROUP == 2) ? mapa(bar_full, 0) : bar_full;
             const uint32_t peer_empty0 = (CTA_GROUP == 2) ? mapa(bar_empty, 1) : 0u;
-            uint32_t stage = 0, phase = 0;
-            bool ok = true;
+            uint32_t stage = 0, phase = 0, sync_target = 0, sync_wait_at = 0xffffffffu;
+            bool ok = true, sync_waits = true;
             const bool hint_a = (flags & kFlagAEvictLast) != 0;
             const bool hint_b = (flags & (kFlagBEvictFirst | kFlagBEvictLast)) != 0;
             const uint64_t pol_a = l2_policy_evict_last();
@@ -411,6 +456,22 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                 const int32_t row_a = static_cast<int32_t>(mi * kTileM + rank * kBM);    // + mt * kBlockM
                 const int32_t row_b = static_cast<int32_t>(ni * BN + rank * C::kBRows);
                 for (uint32_t kb = u.kb0; kb < u.kb1; ++kb) {
+                    if (tail.wave_sync != nullptr && leader) {
+                        // Synchronisation points of the producers (the first k-block of every tile and every
+                        // sync_kb-th after it): a worker announces that it has reached the point, and sync_lag
+                        // k-blocks later waits until every worker of this wave of tiles has.  Workers that share an
+                        // A or a B panel therefore ask for the same k-block within a few k-block times of each
+                        // other: one's fetch from DRAM is the others' L2 hit, or is merged with theirs on the way to
+                        // L2.  The lag hides the counter's round trip behind loads that are already allowed.  (The
+                        // peer CTA's producer is paced by the relayed empty[s].)
+                        const uint32_t rel = kb - u.kb0;
+                        if (rel == 0 || (tail.sync_kb != 0 && rel % tail.sync_kb == 0)) {
+                            red_relaxed_gpu_add(tail.wave_sync, 1u);
+                            sync_target += min(workers, total_tiles - it * workers);
+                            sync_wait_at = kb + tail.sync_lag;
+                        }
+                        if (kb == sync_wait_at && sync_waits) sync_waits = wait_count_patiently(tail.wave_sync, sync_target);
+                    }
                     if (leader) {
                         // wait until the MMAs that read this stage have completed
                         ok = wait_bar(bar_empty + stage * 8, phase ^ 1u, ctx, kStProducerEmpty);
@@ -498,11 +559,17 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
+#ifdef PG_TEST_SHORT_WAIT
+                const bool withhold = worker == 0 && it == 0 &&
+                                      *reinterpret_cast<volatile int *>(&g_test_withhold_acc_commit) != 0;
+#else
+                constexpr bool withhold = false;
+#endif
                 if constexpr (MT == 2) {
-                    umma_commit<CTA_GROUP>(bar_acc_full);            // both accumulators complete
+                    if (!withhold) umma_commit<CTA_GROUP>(bar_acc_full);            // both accumulators complete
                     acc_phase ^= 1u;
                 } else {
-                    umma_commit<CTA_GROUP>(bar_acc_full + acc * 8);  // accumulator complete
+                    if (!withhold) umma_commit<CTA_GROUP>(bar_acc_full + acc * 8);  // accumulator complete
                     if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
                 }
             }
@@ -1289,9 +1356,14 @@ struct DeviceInfo {
     int sm_count = 0;
     int cc_major = 0;
     int *status_word = nullptr;
+    uint32_t *wave_sync = nullptr;
 };
 
 __device__ int g_gemm_status_word;
+// Counters of the producers' synchronisation, one per launch in flight: a launch takes the next slot (zeroed on its
+// stream just before the kernel), so launches that overlap on different streams do not share one.
+constexpr unsigned kWaveSyncSlots = 32;
+__device__ uint32_t g_wave_sync[kWaveSyncSlots];
 
 DeviceInfo g_dev[kMaxDevices];
 DeviceOnce g_dev_once;
@@ -1311,6 +1383,8 @@ cudaError_t device_info(DeviceInfo **out) {
             void *p = nullptr;
             if ((e2 = cudaGetSymbolAddress(&p, g_gemm_status_word)) != cudaSuccess) return e2;
             d.status_word = static_cast<int *>(p);
+            if ((e2 = cudaGetSymbolAddress(&p, g_wave_sync)) != cudaSuccess) return e2;
+            d.wave_sync = static_cast<uint32_t *>(p);
         }
         g_dev[dev] = d;
         return cudaSuccess;
@@ -1416,7 +1490,7 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
     const uint64_t tiles = m_tiles * n_tiles;
     uint64_t workers = static_cast<uint64_t>(sms / CTA_GROUP);
 
-    TailArgs tail = {static_cast<uint32_t>(tiles), 0u, nullptr, nullptr};
+    TailArgs tail = {static_cast<uint32_t>(tiles), 0u, nullptr, nullptr, nullptr, 0u, 0u};
     if (CTA_GROUP == 2 && BN == 256 && MT == 1 && g.workspace && g.n_extra_dst == 0) {
         uint32_t full = 0, split = 0;
         size_t need = 0;
@@ -1451,6 +1525,23 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
     // one tile row (m <= 128): every weight byte is read exactly once, so B streams through L2 (evict first)
     const uint32_t shape_flags = (CTA_GROUP == 1 && g.m <= 128) ? kFlagBEvictFirst : 0u;
     const uint32_t flags = env_flags >= 0 ? static_cast<uint32_t>(env_flags) : (kDefaultFlags | shape_flags);
+    // Producer synchronisation (see the producer role): for problems of at least two waves of tiles and about 0.2
+    // TFLOP, where keeping the workers in step pays for the 4-byte memset in front of the launch.  Measured on B200
+    // against the same kernel without it: 8192^3 +1 %, 8192 x 32768 x 16384 +2-4 %, 32768 x 32768 x 16384 +9 % (DRAM
+    // reads of the second shape 8.9-12.4 -> 6.4 GB, requests merged on the way to L2 x 3-5).
+    // PEAKGEMM_TUNE_WAVESYNC (builds with PG_ENABLE_TUNING only): 0 off, 1 on, -1 automatic.
+    static const int env_wave = tune_env_int("PEAKGEMM_TUNE_WAVESYNC", -1);
+    const bool wave_auto = tiles >= 2 * workers && g.k >= 2048 &&
+                           static_cast<double>(g.m) * static_cast<double>(g.n) * static_cast<double>(g.k) >= 1.0e11;
+    if ((env_wave > 0 || (env_wave < 0 && wave_auto)) && tail.split < 2 && tiles > workers && d.wave_sync) {
+        static std::atomic<unsigned> slot_counter{0};
+        uint32_t *ctr = d.wave_sync + (slot_counter.fetch_add(1) % kWaveSyncSlots);
+        if (cudaMemsetAsync(ctr, 0, sizeof(uint32_t), stream) == cudaSuccess) tail.wave_sync = ctr;
+        static const int env_sync_kb = tune_env_int("PEAKGEMM_TUNE_SYNC_KB", 8);
+        tail.sync_kb = static_cast<uint32_t>(env_sync_kb);
+        static const int env_sync_lag = tune_env_int("PEAKGEMM_TUNE_SYNC_LAG", 1);
+        tail.sync_lag = static_cast<uint32_t>(env_sync_lag);
+    }
     if (tail.split >= 2) {
         // Owners wait for helper CTAs of the same grid: ask for a cooperative launch, which starts the grid only
         // when all of it can be resident at once.  If the device refuses, run without the split.
@@ -1463,7 +1554,7 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
         if (e == cudaSuccess) return e;
         cudaGetLastError();
         --cfg.numAttrs;
-        tail = TailArgs{static_cast<uint32_t>(tiles), 0u, nullptr, nullptr};
+        tail = TailArgs{static_cast<uint32_t>(tiles), 0u, nullptr, nullptr, nullptr, 0u, 0u};
     }
     return cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b, tm_c, n_dst, static_cast<uint32_t>(g.m),
                               static_cast<uint32_t>(g.n), static_cast<uint32_t>(g.k), group_m, flags,
@@ -1772,3 +1863,10 @@ int gemm_device_status(int *out, cudaStream_t stream, cudaError_t *cuda_err) {
 }
 
 }  // namespace pg
+
+#ifdef PG_TEST_SHORT_WAIT
+// Test build only: 1 = the first worker's MMA issuer withholds the "accumulator ready" signal of its first tile.
+extern "C" int pg_test_withhold_gemm_signal(int on) {
+    return static_cast<int>(cudaMemcpyToSymbol(pg::g_test_withhold_acc_commit, &on, sizeof(int)));
+}
+#endif

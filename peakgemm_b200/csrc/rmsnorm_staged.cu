@@ -49,7 +49,15 @@ template <bool BWD> struct RowIndex { using type = int64_t; };
 template <> struct RowIndex<true> { using type = int; };
 constexpr int kMaxStages = 16;
 constexpr int kGammaRegsMaxVpt = 4;     // forward: gamma in registers up to this many vectors per thread
+#ifdef PG_TEST_SHORT_WAIT
+// Test build (libPeakGemm_device_waittest.so, never shipped as the product): waits give up after 2 ms, and a
+// switch in device memory makes the first CTA's producer leave out its LAST row (no copy, no arrival), so that the
+// consumer group waiting for that row exercises the give-up path with no copy in flight.
+constexpr uint64_t kWaitTimeoutNs = 2000000ull;
+__device__ int g_test_withhold_last_row;
+#else
 constexpr uint64_t kWaitTimeoutNs = 2000000000ull;
+#endif
 constexpr uint32_t kSmemBudget = 200 * 1024;      // bytes of dynamic shared memory we ask for at most
 
 enum : int { kStRmsProducer = 11, kStRmsConsumer = 12 };
@@ -211,6 +219,11 @@ rms_staged_kernel(uint4 *__restrict__ out, float *__restrict__ partial, const ui
             uint32_t phase = 0;
             const uint64_t pol = l2_policy_evict_first();     // every row is read exactly once
             for (int64_t i = 0; i < my_rows; ++i) {
+#ifdef PG_TEST_SHORT_WAIT
+                if (blockIdx.x == 0 && i == my_rows - 1 &&
+                    *reinterpret_cast<volatile int *>(&g_test_withhold_last_row) != 0)
+                    break;
+#endif
                 if (!wait_bar(bar_empty + slot * 8, phase ^ 1u, ctx, kStRmsProducer)) break;
                 const int64_t row = blockIdx.x + i * gridDim.x;
                 mbar_arrive_expect_tx(bar_full + slot * 8, L.slot_bytes);
@@ -557,3 +570,10 @@ cudaError_t rmsnorm_device_status(int *out, cudaStream_t stream) {
 }
 
 }  // namespace pg
+
+#ifdef PG_TEST_SHORT_WAIT
+// Test build only: 1 = the first CTA's producer leaves out its last row.
+extern "C" int pg_test_withhold_rmsnorm_row(int on) {
+    return static_cast<int>(cudaMemcpyToSymbol(pg::g_test_withhold_last_row, &on, sizeof(int)));
+}
+#endif

@@ -201,3 +201,91 @@ class ShardedGemm:
         for (r0, r1), band in zip(spans, views):
             out3[r0:r1].copy_(band.transpose(0, 1))      # block r -> columns [r*nl, (r+1)*nl)
         return out
+
+
+# ------------------------------------------------------------------ RMSNorm ----
+
+def row_shard(rows: int, world: int, rank: int) -> tuple[int, int]:
+    """Rows [start, stop) of x (and dy, y, dx) that `rank` owns: contiguous blocks of ceil(rows / world) rows,
+    the last non-empty one possibly shorter; their union is [0, rows)."""
+    if rows < 0 or world < 1 or not (0 <= rank < world):
+        raise ValueError("bad shard request")
+    per = -(-rows // world)
+    start = min(rows, rank * per)
+    return start, min(rows, start + per)
+
+
+def _default_rms_fwd(y, x, gamma, eps):
+    from . import capi   # the CUDA path; there is no fallback
+
+    capi.rmsnorm_fwd(y, x, gamma, eps)
+
+
+def _default_rms_bwd(dx, dgamma, dy, x, gamma, eps):
+    from . import capi
+
+    ws = torch.empty(max(1, capi.rmsnorm_bwd_workspace_bytes(x.shape[0], x.shape[1]) // 4), device=x.device)
+    capi.rmsnorm_bwd(dx, dgamma, dy, x, gamma, ws, eps)
+
+
+class ShardedRmsNorm:
+    """RMSNorm forward / backward with the ROWS of x sharded over the ranks of `group` (gamma replicated).
+
+    The reference project has neither RMSNorm nor multi-GPU code; the split follows from the operator: every row
+    is normalised on its own, so y and dx need no communication at all.  Only dgamma = sum over ALL rows of
+    dy * xhat crosses ranks, and only when the caller wants the global sum:
+
+      reduce="none"        dgamma holds this rank's partial sum (a data-parallel caller that reduces gradients
+                           itself, bucketed with its other parameters, wants exactly this);
+      reduce="all_reduce"  one all-reduce(SUM) of the [h] fp32 vector (16-32 KiB: latency-bound).  The order of
+                           the additions is the collective library's: reproducible for a fixed world size and
+                           algorithm, not specified otherwise;
+      reduce="ordered"     all-gather of the partial vectors, summed in rank order on every rank: every rank gets
+                           bit-identical dgamma, in an order that does not depend on the collective's algorithm.
+
+    `fwd(y, x, gamma, eps)` and `bwd(dx, dgamma, dy, x, gamma, eps)` compute on this rank's rows in place; they
+    default to the sm_100a kernels through the C ABI.  Tests on CPU ranks (gloo) pass the oracle here.
+    """
+
+    def __init__(self, rows: int, group=None, fwd=None, bwd=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.rows = rows
+        self.start, self.stop = row_shard(rows, self.world, self.rank)
+        self.fwd = fwd or _default_rms_fwd
+        self.bwd = bwd or _default_rms_bwd
+
+    @property
+    def rows_local(self) -> int:
+        return self.stop - self.start
+
+    def forward(self, x_local: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-6,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+        """y for this rank's rows.  No communication."""
+        assert x_local.shape[0] == self.rows_local
+        y = out if out is not None else torch.empty_like(x_local)
+        if self.rows_local:
+            self.fwd(y, x_local, gamma, eps)
+        return y
+
+    def backward(self, dy_local: torch.Tensor, x_local: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-6,
+                 reduce: str = "all_reduce"):
+        """(dx for this rank's rows, dgamma [h] fp32 reduced as `reduce` says)."""
+        if reduce not in ("none", "all_reduce", "ordered"):
+            raise ValueError(reduce)
+        assert x_local.shape[0] == self.rows_local and dy_local.shape == x_local.shape
+        dx = torch.empty_like(x_local)
+        dgamma = torch.zeros(x_local.shape[1], dtype=torch.float32, device=x_local.device)
+        if self.rows_local:
+            self.bwd(dx, dgamma, dy_local, x_local, gamma, eps)
+        if self.world > 1 and reduce == "all_reduce":
+            dist.all_reduce(dgamma, op=dist.ReduceOp.SUM, group=self.group)
+        elif self.world > 1 and reduce == "ordered":
+            parts = torch.empty(self.world, dgamma.numel(), dtype=torch.float32, device=dgamma.device)
+            dist.all_gather_into_tensor(parts.view(-1), dgamma, group=self.group)
+            total = parts[0].clone()
+            for r in range(1, self.world):          # rank order, the same on every rank
+                total += parts[r]
+            dgamma = total
+        return dx, dgamma

@@ -82,21 +82,108 @@ def _worker(rank, world, port, m, n, k, bands, errors):
         raise
 
 
-@pytest.mark.parametrize("bands", [1, 3])
-def test_sharded_gemm_two_ranks(bands):
+def _run_ranks(target, args, world=2, timeout=120):
+    """Runs `target(rank, world, port, *args, errors)` on `world` spawned CPU ranks; no rank is left behind."""
     ctx = mp.get_context("spawn")
     errors = ctx.SimpleQueue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, 600, 256, 64, bands, errors)) for r in range(2)]
-    for p in procs:
-        p.start()
-    for p in procs:
-        p.join(120)
+    procs = [ctx.Process(target=target, args=(r, world, port, *args, errors)) for r in range(world)]
+    try:
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(timeout)
+    finally:
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+                p.join(5)
+                if p.is_alive():
+                    p.kill()
     msgs = []
     while not errors.empty():
         msgs.append(errors.get())
     assert not msgs, msgs
     assert all(p.exitcode == 0 for p in procs)
+
+
+@pytest.mark.parametrize("m,n,k,bands", [
+    (600, 256, 64, 1),
+    (600, 256, 64, 3),
+    (1024, 1024, 128, 2),     # tiles like the sharded benchmark shape: each rank's block is whole 512 x 256 tiles
+])
+def test_sharded_gemm_two_ranks(m, n, k, bands):
+    _run_ranks(_worker, (m, n, k, bands))
+
+
+def _oracle_rms_fwd(y, x, gamma, eps):
+    import oracle
+
+    y.copy_(oracle.rmsnorm_fwd(x, gamma, eps).to(y.dtype))
+
+
+def _oracle_rms_bwd(dx, dgamma, dy, x, gamma, eps):
+    import oracle
+
+    d, g = oracle.rmsnorm_bwd(dy, x, gamma, eps)
+    dx.copy_(d.to(dx.dtype))
+    dgamma.copy_(g)
+
+
+def _rms_worker(rank, world, port, rows, h, errors):
+    try:
+        sys.path.insert(0, REPO)
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        import oracle
+        from peakgemm_b200.dist import ShardedRmsNorm
+
+        x, dy, gamma = oracle.rmsnorm_inputs(rows, h, torch.bfloat16, 3)     # every rank draws the same tensors
+        y_ref = oracle.rmsnorm_fwd(x, gamma).to(torch.bfloat16)
+        dx_ref, dg_ref = oracle.rmsnorm_bwd(dy, x, gamma)
+        sn = ShardedRmsNorm(rows, fwd=_oracle_rms_fwd, bwd=_oracle_rms_bwd)
+        xs, dys = x[sn.start:sn.stop].contiguous(), dy[sn.start:sn.stop].contiguous()
+        assert torch.equal(sn.forward(xs, gamma), y_ref[sn.start:sn.stop])
+        dx, dg_local = sn.backward(dys, xs, gamma, reduce="none")
+        assert torch.equal(dx, dx_ref[sn.start:sn.stop].to(torch.bfloat16))
+        _, dg_local_ref = oracle.rmsnorm_bwd(dys, xs, gamma)
+        assert torch.equal(dg_local, dg_local_ref)
+        for how in ("all_reduce", "ordered"):
+            _, dg = sn.backward(dys, xs, gamma, reduce=how)
+            assert (dg - dg_ref).abs().max().item() <= 1e-3 * dg_ref.abs().max().item()
+            everyone = [torch.empty_like(dg) for _ in range(world)]
+            dist.all_gather(everyone, dg)
+            if how == "ordered":           # rank-ordered sum: the same bits on every rank
+                assert all(torch.equal(everyone[0], e) for e in everyone)
+        with pytest.raises(ValueError):
+            sn.backward(dys, xs, gamma, reduce="tree")
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as e:  # noqa: BLE001
+        errors.put(f"rank {rank}: {e!r}")
+        raise
+
+
+@pytest.mark.parametrize("rows,h,world", [(64, 256, 2), (37, 128, 2), (5, 64, 3)])
+def test_sharded_rmsnorm_ranks(rows, h, world):
+    """Rows split over the ranks (ragged last block, and a rank with fewer rows than the others); dgamma local,
+    all-reduced and rank-ordered."""
+    _run_ranks(_rms_worker, (rows, h), world=world)
+
+
+def test_row_shard_properties():
+    sys.path.insert(0, REPO)
+    from peakgemm_b200.dist import row_shard
+
+    for rows in (0, 1, 5, 64, 1000, 32768):
+        for world in (1, 2, 3, 8):
+            spans = [row_shard(rows, world, r) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == rows
+            for (s0, e0), (s1, e1) in zip(spans, spans[1:]):
+                assert e0 == s1 and s0 <= e0
+    assert row_shard(32768, 8, 7) == (28672, 32768)
+    with pytest.raises(ValueError):
+        row_shard(8, 2, 2)
 
 
 def test_single_process_is_one_shard():

@@ -95,7 +95,7 @@ def test_config1_exact_vs_fp32_matmul():
     a, b = oracle.gemm_inputs_uniform(2048, 2048, 2048, torch.bfloat16, 0)
     exact = oracle.gemm_exact_acc(a, b)
     fast = oracle.gemm_fp32(a, b)
-    assert abs(float(fast.abs().max()) - 81.44) < 0.5          # the survey's figure for this seed
+    assert abs(float(fast.abs().max()) - 81.44) < 0.5          # max|C| of this seed: pins the input generator
     assert (exact - fast).abs().max().item() < 1e-3 * oracle.gemm_tolerance(2048, fast)
 
 
