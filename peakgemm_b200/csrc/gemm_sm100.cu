@@ -115,6 +115,13 @@ enum : uint32_t {
     kFlagBEvictLast = 16u,       // B loads carry an L2 evict-last hint
     kFlagSerpentine = 32u,       // odd bands walk their columns right to left
     kFlagRasterAlongN = 64u,     // bands of group_m tile COLUMNS walked row by row: consecutive workers share an A panel
+    // Launched under programmatic stream serialisation: the grid lets its successor in the stream start at once
+    // (griddepcontrol.launch_dependents) and itself touches no global memory before its predecessor has completed
+    // (griddepcontrol.wait at the start of every role that loads or stores).  Back-to-back GEMMs then overlap the
+    // launch latency and the set-up of one kernel (barriers, tensor-memory allocation, descriptor prefetch) with the
+    // last tiles of the one before.  Behind any other kernel the wait returns when that kernel has completed: the
+    // ordinary stream order.
+    kFlagPdl = 128u,
 };
 
 // Codes written to the device status word (role that gave up).
@@ -136,6 +143,9 @@ struct Cfg {
     // MT == 1: two accumulators, tile i's epilogue overlaps tile i+1's main loop.
     // MT == 2: the two row blocks' accumulators fill tensor memory; both belong to the tile in flight.
     static constexpr uint32_t kTmemCols = 2 * BN;
+    // Columns of one TMA store box.  MT == 2: 8 epilogue warps share the staging area, 4 KiB each; two 32 x 32
+    // boxes (64-byte swizzle) per warp let the conversion of one box overlap the store of the other.
+    static constexpr uint32_t kStoreBoxCols = (MT == 2) ? 32 : kStoreCols;
     static_assert(MT == 1 || (MT == 2 && CTA_GROUP == 2 && BN == 256), "two row blocks: CTA pair, 256 columns");
     static constexpr uint32_t kOffA = 0;
     static constexpr uint32_t kOffB = kOffA + STAGES * kABytes;
@@ -275,7 +285,7 @@ struct TailArgs {
     uint32_t split;
     float *ws;
     uint32_t *flags;
-    uint32_t *wave_sync;    // null, or a zeroed counter: the producers keep the workers within one tile of each other
+    uint32_t *wave_sync;    // null, or a zeroed pair {arrivals, workers checked out}: the producers keep in step
     uint32_t sync_kb;       // k-blocks between two synchronisation points inside a tile (0: only at the tile's start)
     uint32_t sync_lag;      // the wait for a point comes this many k-blocks after the arrival at it
 };
@@ -434,11 +444,14 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
     }
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot_gen;
+    const bool pdl = (flags & kFlagPdl) != 0;
+    if (pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // -------------------------------------------------------------- roles ----
     if (warp == 0) {
         if (lane == 0) {
             // ===== producer =====
+            if (pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
             // In a pair, both CTAs' loads complete on the LEADER's full[s].
             const uint32_t full0 = (CTA_GROUP == 2) ? mapa(bar_full, 0) : bar_full;
             const uint32_t peer_empty0 = (CTA_GROUP == 2) ? mapa(bar_empty, 1) : 0u;
@@ -576,6 +589,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         }
         __syncwarp();
     } else {
+        if (pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
         if constexpr (MT == 2) {
             // ===== epilogue, two row blocks per CTA: 8 warps =====
             // Warp w reads lane quarter w % 4 (the hardware rule) and column half (w - 2) / 4 of each accumulator:
@@ -583,13 +597,13 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
             // back to the MMA warp before anything is converted or stored, accumulator 0 first, so the next tile's
             // first row block restarts while accumulator 1 is still being read.
             const uint32_t q = warp & 3u;
-            const uint32_t e = warp - 2u;                 // 0..7: one 32 x 64 staging box each
+            const uint32_t e = warp - 2u;                 // 0..7: 4 KiB of staging each = two 32 x 32 boxes
             const uint32_t half = e >> 2;                 // columns [128 * half, 128 * half + 128)
             const uint32_t sbuf = smem_base + C::kOffC + e * kStageBufBytes;
             uint8_t *sbuf_gen = smem_gen + C::kOffC + e * kStageBufBytes;
             const uint32_t acc_empty_leader = mapa(bar_acc_empty, 0);
             const uint32_t peer_acc_full = mapa(bar_acc_full, 1);
-            uint32_t acc_phase = 0;
+            uint32_t acc_phase = 0, nbuf = 0;
             bool ok = true;
             const uint64_t pol_store = l2_policy_evict_first();
             const bool fused = epi.any();
@@ -619,53 +633,57 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                     if (lane == 0) mbar_arrive_cluster(acc_empty_leader + mt * 8);
                     const bool row_ok = row0 + lane < M;
                     const float rs = fused ? epi_row_scale(epi, row_ok, row0 + lane) : 1.f;
-    #pragma unroll
-                    for (uint32_t cb = 0; cb < 2; ++cb) {       // two 32 x 64 boxes
-                        const uint32_t col0 = ni * BN + half * 128u + cb * kStoreCols;
+#pragma unroll
+                    for (uint32_t cb = 0; cb < 4; ++cb) {       // four 32 x 32 boxes, two staging buffers in turn
+                        const uint32_t col0 = ni * BN + half * 128u + cb * 32u;
                         if (fused) {
-    #pragma unroll
-                            for (uint32_t c = 0; c < 8; ++c) {
+#pragma unroll
+                            for (uint32_t c = 0; c < 4; ++c) {
                                 if (col0 + c * 8u < N) {      // n is a multiple of 8: a group of 8 columns is in or out
                                     float f[8];
-    #pragma unroll
-                                    for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[2 * cb + (c >> 2)][(c & 3u) * 8u + i]);
+#pragma unroll
+                                    for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[cb][c * 8u + i]);
                                     epi_apply8<BF16>(f, rs, epi, row_ok, row0 + lane, col0 + c * 8u);
-    #pragma unroll
-                                    for (int i = 0; i < 8; ++i) v[2 * cb + (c >> 2)][(c & 3u) * 8u + i] = __float_as_uint(f[i]);
+#pragma unroll
+                                    for (int i = 0; i < 8; ++i) v[cb][c * 8u + i] = __float_as_uint(f[i]);
                                 }
                             }
                         }
-                        uint4 o[8];
-    #pragma unroll
-                        for (uint32_t c = 0; c < 8; ++c) {
-                            const uint32_t *src = &v[2 * cb + (c >> 2)][(c & 3u) * 8u];
+                        uint4 o[4];
+#pragma unroll
+                        for (uint32_t c = 0; c < 4; ++c) {
+                            const uint32_t *src = &v[cb][c * 8u];
                             o[c].x = pack2<BF16>(__uint_as_float(src[0]), __uint_as_float(src[1]));
                             o[c].y = pack2<BF16>(__uint_as_float(src[2]), __uint_as_float(src[3]));
                             o[c].z = pack2<BF16>(__uint_as_float(src[4]), __uint_as_float(src[5]));
                             o[c].w = pack2<BF16>(__uint_as_float(src[6]), __uint_as_float(src[7]));
                         }
-                        // the previous store from this box must have finished reading it
-                        if (lane == 0) bulk_wait_group_read<0>();
+                        // the store issued two boxes ago from this buffer must have finished reading it
+                        if (lane == 0) bulk_wait_group_read<1>();
                         __syncwarp();
-                        // row `lane`, 8 chunks of 16 bytes, chunk c stored at position c ^ (row % 8)  (128-byte swizzle)
-    #pragma unroll
-                        for (uint32_t c = 0; c < 8; ++c)
-                            *reinterpret_cast<uint4 *>(sbuf_gen + lane * 128u + ((c ^ (lane & 7u)) << 4)) = o[c];
+                        const uint32_t box = sbuf + nbuf * (kStageBufBytes / 2);
+                        uint8_t *box_gen = sbuf_gen + nbuf * (kStageBufBytes / 2);
+                        // row `lane` = 64 bytes, 4 chunks of 16 bytes, chunk c stored at position c ^ ((row / 2) % 4)
+                        // (the 64-byte swizzle: address bits 4-5 xor bits 7-8)
+#pragma unroll
+                        for (uint32_t c = 0; c < 4; ++c)
+                            *reinterpret_cast<uint4 *>(box_gen + lane * 64u + ((c ^ ((lane >> 1) & 3u)) << 4)) = o[c];
                         fence_proxy_async_smem();
                         __syncwarp();
                         if (lane == 0) {
                             if (row0 < M && col0 < N) {
                                 for (uint32_t d = 0; d < n_dst; ++d) {
                                     if (flags & kFlagStoreEvictFirst)
-                                        tma_store_2d_hint(&tm_c.m[d], sbuf, static_cast<int32_t>(col0),
+                                        tma_store_2d_hint(&tm_c.m[d], box, static_cast<int32_t>(col0),
                                                           static_cast<int32_t>(row0), pol_store);
                                     else
-                                        tma_store_2d(&tm_c.m[d], sbuf, static_cast<int32_t>(col0),
+                                        tma_store_2d(&tm_c.m[d], box, static_cast<int32_t>(col0),
                                                      static_cast<int32_t>(row0));
                                 }
                             }
                             bulk_commit_group();
                         }
+                        nbuf ^= 1u;
                     }
                 }
                 acc_phase ^= 1u;
@@ -839,6 +857,15 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
     if (warp == 1) {
         tc_fence_after_sync();
         tmem_dealloc<CTA_GROUP>(tmem_base, C::kTmemCols);
+    }
+    // Producer synchronisation: the counter pair is handed back zeroed.  Every worker's producer has left its loop
+    // before its CTA gets here, so when the last worker checks out nobody reads the counter any more.
+    if (tail.wave_sync != nullptr && leader && threadIdx.x == 0) {
+        if (atomicAdd(tail.wave_sync + 1, 1u) == workers - 1u) {
+            tail.wave_sync[0] = 0u;
+            tail.wave_sync[1] = 0u;
+            __threadfence();
+        }
     }
 }
 
@@ -1297,16 +1324,16 @@ EncodeTiledFn get_encode_fn() {
 
 // Row-major [rows, cols] 16-bit matrix with row pitch ld (elements); box = box_rows x 64 columns.
 bool encode_tmap(CUtensorMap *tm, const void *base, int64_t rows, int64_t cols, int64_t ld,
-                 uint32_t box_rows, bool bf16, bool is_output) {
+                 uint32_t box_rows, bool bf16, bool is_output, uint32_t box_cols) {
     EncodeTiledFn enc = get_encode_fn();
     if (!enc) return false;
     cuuint64_t gdim[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
     cuuint64_t gstride[1] = {static_cast<cuuint64_t>(ld) * 2};
-    cuuint32_t box[2] = {kBK, box_rows};
+    cuuint32_t box[2] = {box_cols, box_rows};     // 64 columns: 128-byte swizzle; 32 columns: 64-byte swizzle
     cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
                      const_cast<void *>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     CU_TENSOR_MAP_SWIZZLE_128B,
+                     box_cols == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
                      is_output ? CU_TENSOR_MAP_L2_PROMOTION_NONE : CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
@@ -1320,7 +1347,7 @@ struct TmapKey {
     const void *base;
     int64_t rows, cols, ld;
     uint32_t box_rows;
-    uint32_t kind;   // bit 0: bf16, bit 1: output
+    uint32_t kind;   // bit 0: bf16, bit 1: output, bit 2: 32-column box
     bool operator==(const TmapKey &o) const {
         return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows &&
                kind == o.kind;
@@ -1334,14 +1361,15 @@ struct TmapSlot {
 constexpr int kTmapSlots = 32;
 
 bool make_tmap(CUtensorMap *tm, const void *base, int64_t rows, int64_t cols, int64_t ld,
-               uint32_t box_rows, bool bf16, bool is_output) {
+               uint32_t box_rows, bool bf16, bool is_output, uint32_t box_cols = kBK) {
     thread_local TmapSlot cache[kTmapSlots] = {};
-    const TmapKey key{base, rows, cols, ld, box_rows, (bf16 ? 1u : 0u) | (is_output ? 2u : 0u)};
+    const TmapKey key{base, rows, cols, ld, box_rows,
+                      (bf16 ? 1u : 0u) | (is_output ? 2u : 0u) | (box_cols == 32 ? 4u : 0u)};
     uint64_t h = reinterpret_cast<uint64_t>(base) >> 8;
     h ^= static_cast<uint64_t>(rows) * 0x9E3779B97F4A7C15ull + static_cast<uint64_t>(cols) * 31 + box_rows + key.kind;
     TmapSlot &slot = cache[(h ^ (h >> 17)) % kTmapSlots];
     if (!(slot.valid && slot.key == key)) {
-        if (!encode_tmap(&slot.map, base, rows, cols, ld, box_rows, bf16, is_output)) {
+        if (!encode_tmap(&slot.map, base, rows, cols, ld, box_rows, bf16, is_output, box_cols)) {
             slot.valid = false;
             return false;
         }
@@ -1363,7 +1391,7 @@ __device__ int g_gemm_status_word;
 // Counters of the producers' synchronisation, one per launch in flight: a launch takes the next slot (zeroed on its
 // stream just before the kernel), so launches that overlap on different streams do not share one.
 constexpr unsigned kWaveSyncSlots = 32;
-__device__ uint32_t g_wave_sync[kWaveSyncSlots];
+__device__ uint32_t g_wave_sync[2 * kWaveSyncSlots];      // zero at load; every kernel leaves its pair zeroed
 
 DeviceInfo g_dev[kMaxDevices];
 DeviceOnce g_dev_once;
@@ -1477,10 +1505,10 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
     DstMaps tm_c = {};
     if (!make_tmap(&tm_a, g.a, g.m, g.k, g.lda, kBM, BF16, false) ||
         !make_tmap(&tm_b, g.b, g.n, g.k, g.ldb, C::kBRows, BF16, false) ||
-        !make_tmap(&tm_c.m[0], g.c, g.m, g.n, g.ldc, kStoreRows, BF16, true))
+        !make_tmap(&tm_c.m[0], g.c, g.m, g.n, g.ldc, kStoreRows, BF16, true, C::kStoreBoxCols))
         return cudaErrorInvalidValue;
     for (int i = 0; i < g.n_extra_dst; ++i)
-        if (!make_tmap(&tm_c.m[1 + i], g.extra_dst[i], g.m, g.n, g.ldc, kStoreRows, BF16, true))
+        if (!make_tmap(&tm_c.m[1 + i], g.extra_dst[i], g.m, g.n, g.ldc, kStoreRows, BF16, true, C::kStoreBoxCols))
             return cudaErrorInvalidValue;
     const uint32_t n_dst = 1u + static_cast<uint32_t>(g.n_extra_dst);
 
@@ -1526,7 +1554,7 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
     const uint32_t shape_flags = (CTA_GROUP == 1 && g.m <= 128) ? kFlagBEvictFirst : 0u;
     const uint32_t flags = env_flags >= 0 ? static_cast<uint32_t>(env_flags) : (kDefaultFlags | shape_flags);
     // Producer synchronisation (see the producer role): for problems of at least two waves of tiles and about 0.2
-    // TFLOP, where keeping the workers in step pays for the 4-byte memset in front of the launch.  Measured on B200
+    // TFLOP.  Measured on B200
     // against the same kernel without it: 8192^3 +1 %, 8192 x 32768 x 16384 +2-4 %, 32768 x 32768 x 16384 +9 % (DRAM
     // reads of the second shape 8.9-12.4 -> 6.4 GB, requests merged on the way to L2 x 3-5).
     // PEAKGEMM_TUNE_WAVESYNC (builds with PG_ENABLE_TUNING only): 0 off, 1 on, -1 automatic.
@@ -1535,8 +1563,7 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
                            static_cast<double>(g.m) * static_cast<double>(g.n) * static_cast<double>(g.k) >= 1.0e11;
     if ((env_wave > 0 || (env_wave < 0 && wave_auto)) && tail.split < 2 && tiles > workers && d.wave_sync) {
         static std::atomic<unsigned> slot_counter{0};
-        uint32_t *ctr = d.wave_sync + (slot_counter.fetch_add(1) % kWaveSyncSlots);
-        if (cudaMemsetAsync(ctr, 0, sizeof(uint32_t), stream) == cudaSuccess) tail.wave_sync = ctr;
+        tail.wave_sync = d.wave_sync + 2 * (slot_counter.fetch_add(1) % kWaveSyncSlots);
         static const int env_sync_kb = tune_env_int("PEAKGEMM_TUNE_SYNC_KB", 8);
         tail.sync_kb = static_cast<uint32_t>(env_sync_kb);
         static const int env_sync_lag = tune_env_int("PEAKGEMM_TUNE_SYNC_LAG", 1);
@@ -1556,8 +1583,18 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
         --cfg.numAttrs;
         tail = TailArgs{static_cast<uint32_t>(tiles), 0u, nullptr, nullptr, nullptr, 0u, 0u};
     }
+    // An ordinary (not cooperative) launch goes out under programmatic stream serialisation, see kFlagPdl.  Not
+    // when the caller chained this GEMM behind the kernel that produces row_scale: that mode has its own, later wait.
+    uint32_t launch_flags = flags;
+    static const int env_pdl = tune_env_int("PEAKGEMM_TUNE_PDL", 1);
+    if (env_pdl && !(g.pdl_wait && g.row_scale)) {
+        attr[cfg.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[cfg.numAttrs].val.programmaticStreamSerializationAllowed = 1;
+        ++cfg.numAttrs;
+        launch_flags |= kFlagPdl;
+    }
     return cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b, tm_c, n_dst, static_cast<uint32_t>(g.m),
-                              static_cast<uint32_t>(g.n), static_cast<uint32_t>(g.k), group_m, flags,
+                              static_cast<uint32_t>(g.n), static_cast<uint32_t>(g.k), group_m, launch_flags,
                               make_epi(g), tail, d.status_word);
 }
 
