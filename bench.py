@@ -271,11 +271,14 @@ def shape_sweep(peaks: dict) -> list:
     shapes = [("config2", s, s, s, dt) for s in (2048, 4096, 8192, 16384) for dt in (torch.float16, torch.bfloat16)]
     shapes += [("config3", m, n, k, torch.bfloat16) for m in (16, 128, 1024, 4096)
                for (n, k) in ((4096, 4096), (14336, 4096), (4096, 14336), (128256, 4096))]
+    # the sharded benchmark shape (configs[4]): one of 8 ranks' blocks, a quarter of the problem, the whole problem
+    shapes += [("config5", 32768, 4096, 16384, torch.bfloat16), ("config5", 8192, 32768, 16384, torch.bfloat16),
+               ("config5", 32768, 32768, 16384, torch.bfloat16)]
     rows = []
     g = torch.Generator(device="cuda").manual_seed(2)
     for tag, m, n, k, dt in shapes:
         nbuf = max(1, min(16, -(-(256 << 20) // (2 * n * k))))
-        if tag == "config2":
+        if tag in ("config2", "config5"):
             a = (torch.rand(m, k, device="cuda", generator=g) * 2 - 1).to(dt)
             bs = [(torch.rand(n, k, device="cuda", generator=g) * 2 - 1).to(dt) for _ in range(nbuf)]
         else:
@@ -305,7 +308,8 @@ def shape_sweep(peaks: dict) -> list:
         rows.append({"config": tag, "dtype": str(dt)[6:], "m": m, "n": n, "k": k, "weight_sets": nbuf,
                      "ours_us": t_o * 1e3, "cublas_us": t_c * 1e3, "ours_tflops": fl / t_o / 1e9,
                      "ours_gbs": by / t_o / 1e6, "roofline_us": t_roof * 1e3, "frac_of_roofline": t_roof / t_o,
-                     "speed_vs_cublas": t_c / t_o, "tail_split_workspace_bytes": need})
+                     "speed_vs_cublas": t_c / t_o, "tail_split_workspace_bytes": need,
+                     "persistent_config": list(capi.hgemm_config(m, n, k)) if m > 128 else None})
         del a, bs, cs
     assert capi.device_status() == 0
     return rows
@@ -495,7 +499,8 @@ def config5_block(world: int, rank: int, steps: int = 3) -> dict:
     """benchmark config 5 on the ranks of this run, as part of the default JSON line: m = n = 32768, k = 16384 bf16,
     B column-sharded over the ranks with A replicated (STRONG scaling: the problem is fixed, N = 1 is the
     denominator).  Timed without a gather, with the NCCL all-gather (native shard-major result, and copied to
-    row-major) and with the gather fused into the GEMM epilogue (row-major on every rank, peer stores).  CUDA events,
+    row-major), with the gather fused into the GEMM epilogue as peer stores (row-major on every rank) and as stores that
+    the NVLink switch replicates (multicast).  CUDA events,
     max over ranks.  `parity`: 16 sampled rows of this rank's block against an fp32 product of the same inputs
     (acceptance bound), and at N > 1 the fused result against the NCCL result bit for bit."""
     import math
@@ -560,8 +565,26 @@ def config5_block(world: int, rank: int, steps: int = 3) -> dict:
         torch.cuda.synchronize()
         same = torch.equal(fused, nccl)
         ok = ok * int(same)
-        del nccl, fused
+        del fused
         pm.close()
+        # the gather done by the NVLink switch (multimem.st through a multicast mapping), where the machine has one
+        from peakgemm_b200.dist import MulticastMatrix
+
+        try:
+            mm = MulticastMatrix(m, n, torch.bfloat16)
+        except RuntimeError:
+            mm = None
+        if mm is not None:
+            res["multicast_gather_ms"] = timed(lambda: sg.gathered_multicast(mm, a, b), steps)
+            mc = sg.gathered_multicast(mm, a, b)
+            torch.cuda.synchronize()
+            dist.barrier()
+            ok = ok * int(torch.equal(mc, nccl))
+            del mc
+            mm.close()
+        else:
+            res["multicast_gather_ms"] = None
+        del nccl
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         res["gather_bytes_received_per_gpu"] = 2 * m * (n - sg.n_local)
     res["parity"] = bool(ok.item())

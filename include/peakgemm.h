@@ -192,6 +192,24 @@ int pg_hgemm_multi(void *const *c_list, int n_dst, const void *a, const void *b,
                    int dtype, int max_sms, void *stream);
 
 /*
+ * pg_hgemm with the output written through a MULTICAST address: c_multicast is one
+ * virtual address bound to a buffer on every GPU of a group (an NVLink-switch
+ * multicast mapping, e.g. torch symmetric memory's multicast_ptr or
+ * cuMulticastBindMem), offset to this caller's column block; ldc is the row pitch of
+ * the full matrix.  Every 16-byte store (multimem.st) is replicated by the switch
+ * into every GPU's copy, the caller's own included: a column-sharded caller's block
+ * leaves its GPU once instead of once per peer, and after the callers' barrier every
+ * GPU holds the whole row-major C.  Nothing is loaded through the address.
+ * c_local is the same element in the caller's OWN copy (a plain device address); the
+ * kernel does not write through it.  The persistent kernels only; no fused epilogue
+ * terms.  The memory must stay bound until every rank's kernel has completed.
+ * The reference project has no multi-GPU code.
+ */
+int pg_hgemm_mcast(void *c_local, void *c_multicast, const void *a, const void *b,
+                   int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc,
+                   int dtype, int max_sms, void *stream);
+
+/*
  * Buffers that GPUs of other processes can store into (for pg_hgemm_multi), one
  * node.  pg_peer_alloc: cudaMalloc + CUDA IPC export (handle_out receives
  * PG_PEER_HANDLE_BYTES bytes to send to the peers).  pg_peer_open: maps a peer's

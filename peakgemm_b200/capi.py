@@ -29,6 +29,7 @@ SIGNATURES = {
     "pg_hgemm_fused": (_i, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _p, _p, _p, _i64, _i, _i, _p]),
     "pg_rmsnorm_rstd": (_i, [_p, _p, _i64, _i64, ctypes.c_float, _i, _p]),
     "pg_hgemm_multi": (_i, [ctypes.POINTER(_p), _i, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _p]),
+    "pg_hgemm_mcast": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _p]),
     "pg_peer_alloc": (_i, [_sz, ctypes.POINTER(_p), _p]),
     "pg_peer_open": (_i, [_p, ctypes.POINTER(_p)]),
     "pg_peer_close": (_i, [_p]),
@@ -153,6 +154,16 @@ def hgemm_multi(c_ptrs, a, b, ldc: int, n: int | None = None, *, max_sms: int = 
     st = lib().pg_hgemm_multi(arr, len(c_ptrs), a.data_ptr(), b.data_ptr(), m, n, k, a.stride(0) if m > 1 else k,
                               b.stride(0) if n > 1 else k, ldc, dtype_code(a.dtype), max_sms, _stream_ptr(stream))
     check(st, "pg_hgemm_multi")
+
+
+def hgemm_mcast(c_local_ptr: int, c_multicast_ptr: int, a, b, ldc: int, *, max_sms: int = 0, stream=None) -> None:
+    """pg_hgemm_mcast: C block = A @ B^T written through a multicast address (replicated by the NVLink switch)."""
+    m, k = a.shape
+    n = b.shape[0]
+    st = lib().pg_hgemm_mcast(ctypes.c_void_p(int(c_local_ptr)), ctypes.c_void_p(int(c_multicast_ptr)), a.data_ptr(),
+                              b.data_ptr(), m, n, k, a.stride(0) if m > 1 else k, b.stride(0) if n > 1 else k, ldc,
+                              dtype_code(a.dtype), max_sms, _stream_ptr(stream))
+    check(st, "pg_hgemm_mcast")
 
 
 PG_PEER_HANDLE_BYTES = 64

@@ -133,6 +133,24 @@ int pg_hgemm_multi(void *const *c_list, int n_dst, const void *a, const void *b,
     return from_launch(r, e);
 }
 
+int pg_hgemm_mcast(void *c_local, void *c_multicast, const void *a, const void *b, int64_t m, int64_t n, int64_t k,
+                   int64_t lda, int64_t ldb, int64_t ldc, int dtype, int max_sms, void *stream) {
+    if (m < 0 || n < 0 || k < 0 || max_sms < 0) return PG_ERR_BAD_ARG;
+    if (dtype != PG_F16 && dtype != PG_BF16) return PG_ERR_BAD_ARG;
+    if (m == 0 || n == 0) return PG_OK;
+    if (k == 0) return PG_ERR_UNSUPPORTED;
+    if (!a || !b || !c_local || !c_multicast) return PG_ERR_BAD_ARG;
+    if (lda < k || ldb < k || ldc < n) return PG_ERR_BAD_ARG;
+    if (n % 8 != 0 || k % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0 || ldc % 8 != 0) return PG_ERR_UNSUPPORTED;
+    if (m > kMaxDim || n > kMaxDim || k > kMaxDim) return PG_ERR_UNSUPPORTED;
+    if (!aligned16(a) || !aligned16(b) || !aligned16(c_local) || !aligned16(c_multicast)) return PG_ERR_MISALIGNED;
+    pg::GemmArgs g{c_local, a, b, m, n, k, lda, ldb, ldc, dtype == PG_BF16};
+    g.mc_dst = c_multicast;
+    cudaError_t e = cudaSuccess;
+    const int r = pg::hgemm_launch(g, 0, 0, max_sms, static_cast<cudaStream_t>(stream), &e);
+    return from_launch(r, e);
+}
+
 int pg_hgemm_fused(void *d, const void *a, const void *b, int64_t m, int64_t n, int64_t k, int64_t lda,
                    int64_t ldb, int64_t ldd, const float *row_scale, const void *bias, const void *residual,
                    int64_t ldr, int dtype, int flags, void *stream) {

@@ -184,8 +184,36 @@ struct EpiArgs {
                                 // thread that produces it, before that thread hands it to the store)
     uint32_t ldr;
     uint32_t pdl_wait;          // non-zero: griddepcontrol.wait before the first read of row_scale
+    // Non-null: the output goes out through this address instead of the TMA stores.  It is a MULTICAST address
+    // (one mapping bound to a buffer on every GPU of the group): each 16-byte multimem.st is replicated by the
+    // NVLink switch into every GPU's copy, the issuing GPU's own included, so a column-sharded caller's block
+    // leaves the GPU once, not once per peer.  Row pitch ld_mc elements.
+    uint16_t *mc_dst;
+    uint32_t ld_mc;
     __device__ __forceinline__ bool any() const { return row_scale || bias || residual; }
 };
+
+// One staged output box (ROWS x 64 or 32 columns, written with the swizzle of the matching TMA store box) goes to
+// the multicast address: the warp reads it back so that 8 (or 4) lanes cover one row's contiguous bytes and
+// consecutive lane groups consecutive rows, 16 bytes per lane and instruction.
+template <uint32_t BOX_COLS>
+__device__ __forceinline__ void mc_store_box(const uint8_t *box_gen, uint16_t *mc, uint32_t ld, uint32_t row0,
+                                             uint32_t col0, uint32_t M, uint32_t N, uint32_t lane) {
+    constexpr uint32_t kChunks = BOX_COLS / 8;             // 16-byte chunks per row: 8 or 4
+    constexpr uint32_t kRowsPerIt = 32 / kChunks;          // rows one instruction covers: 4 or 8
+    const uint32_t ch = lane % kChunks, r_in = lane / kChunks;
+#pragma unroll
+    for (uint32_t it = 0; it < kStoreRows / kRowsPerIt; ++it) {
+        const uint32_t r = it * kRowsPerIt + r_in;
+        const uint32_t sw = (BOX_COLS == 64) ? (ch ^ (r & 7u)) : (ch ^ ((r >> 1) & 3u));
+        const uint4 v = *reinterpret_cast<const uint4 *>(box_gen + r * (BOX_COLS * 2u) + (sw << 4));
+        if (row0 + r < M && col0 + ch * 8u < N) {
+            uint16_t *dst = mc + static_cast<size_t>(row0 + r) * ld + col0 + ch * 8u;
+            asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};"
+                         ::"l"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+        }
+    }
+}
 
 // Eight consecutive columns starting at `col` of row `row`: f[i] = f[i] * rs + bias + residual.
 template <bool BF16>
@@ -670,7 +698,9 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                             *reinterpret_cast<uint4 *>(box_gen + lane * 64u + ((c ^ ((lane >> 1) & 3u)) << 4)) = o[c];
                         fence_proxy_async_smem();
                         __syncwarp();
-                        if (lane == 0) {
+                        if (epi.mc_dst != nullptr) {
+                            mc_store_box<32>(box_gen, epi.mc_dst, epi.ld_mc, row0, col0, M, N, lane);
+                        } else if (lane == 0) {
                             if (row0 < M && col0 < N) {
                                 for (uint32_t d = 0; d < n_dst; ++d) {
                                     if (flags & kFlagStoreEvictFirst)
@@ -819,7 +849,9 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
-                    if (lane == 0) {
+                    if (epi.mc_dst != nullptr) {
+                        mc_store_box<64>(sbuf_gen, epi.mc_dst, epi.ld_mc, row0, col0, M, N, lane);
+                    } else if (lane == 0) {
                         if (row0 < M && col0 < N) {
                             for (uint32_t d = 0; d < n_dst; ++d) {
                                 if (flags & kFlagStoreEvictFirst)
@@ -843,6 +875,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
             if (n_dst == 1) bulk_wait_group_read<0>();
             else bulk_wait_group<0>();
         }
+        if (epi.mc_dst != nullptr) __threadfence_system();     // the multicast stores are performed before the grid ends
         __syncwarp();
     }
 
@@ -1429,6 +1462,8 @@ EpiArgs make_epi(const GemmArgs &g) {
     e.residual = static_cast<const uint16_t *>(g.residual);
     e.ldr = static_cast<uint32_t>(g.ldr);
     e.pdl_wait = (g.pdl_wait && g.row_scale) ? 1u : 0u;
+    e.mc_dst = static_cast<uint16_t *>(g.mc_dst);
+    e.ld_mc = static_cast<uint32_t>(g.ldc);
     return e;
 }
 
@@ -1519,7 +1554,7 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
     uint64_t workers = static_cast<uint64_t>(sms / CTA_GROUP);
 
     TailArgs tail = {static_cast<uint32_t>(tiles), 0u, nullptr, nullptr, nullptr, 0u, 0u};
-    if (CTA_GROUP == 2 && BN == 256 && MT == 1 && g.workspace && g.n_extra_dst == 0) {
+    if (CTA_GROUP == 2 && BN == 256 && MT == 1 && g.workspace && g.n_extra_dst == 0 && !g.mc_dst) {
         uint32_t full = 0, split = 0;
         size_t need = 0;
         plan_tail(g.m, g.n, g.k, static_cast<int>(workers), &full, &split, &need);
@@ -1791,10 +1826,12 @@ int hgemm_launch(const GemmArgs &g, int variant, int block_n, int max_sms, cudaS
     if (max_sms > 0 && max_sms < sms) sms = max_sms < 2 ? 2 : max_sms;
     // variant 3 = cluster split-K; chosen automatically when one CTA per tile would leave more than
     // 40 % of the SMs without a tile and k is long enough to split
-    if (g.n_extra_dst > 0 && variant == 0)        // several destinations: the persistent TMA-store kernels only
+    const bool staged_store = g.n_extra_dst > 0 || g.mc_dst != nullptr;    // several destinations or a multicast one:
+    if (staged_store && variant == 0)                                       // the persistent kernels only
         choose_config(g, sms, &variant, &block_n);
-    if (g.n_extra_dst > 0 && (variant == 3 || variant == 4)) return kLaunchBadConfig;
-    if (g.n_extra_dst > 0 && (g.row_scale || g.bias || g.residual)) return kLaunchBadConfig;
+    if (staged_store && (variant == 3 || variant == 4)) return kLaunchBadConfig;
+    if (staged_store && (g.row_scale || g.bias || g.residual)) return kLaunchBadConfig;
+    if (g.n_extra_dst > 0 && g.mc_dst != nullptr) return kLaunchBadConfig;
     static const int env_split = tune_env_int("PEAKGEMM_TUNE_SPLITK", -1);
     // variant 4 = skinny kernel (m <= 64, operands swapped); the automatic choice for such m
     static const bool env_no_skinny = tune_env_int("PEAKGEMM_TUNE_SKINNY", 1) == 0;

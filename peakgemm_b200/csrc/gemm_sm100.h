@@ -22,6 +22,8 @@ struct GemmArgs {
     int64_t ldr = 0;
     bool pdl_wait = false;              // the epilogue waits for the preceding kernel of the stream before it reads
                                         // row_scale (programmatic dependent launch); the main loop does not wait
+    void *mc_dst = nullptr;             // non-null: C is written through this multicast address (row pitch ldc) with
+                                        // multimem.st instead of TMA stores to c; c must still be a local address
     void *workspace = nullptr;          // optional scratch for the tail split of the 256-wide CTA-pair kernel
     size_t workspace_bytes = 0;
 };

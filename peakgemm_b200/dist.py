@@ -111,6 +111,42 @@ class PeerMatrix:
             self._own_ptr = 0
 
 
+class MulticastMatrix:
+    """A [rows, cols] 16-bit matrix allocated on every rank in torch's symmetric memory and bound to ONE multicast
+    address: a store through that address is replicated by the NVLink switch into every rank's copy (NVLS).
+
+    The allocation, the handle exchange and the multicast binding are torch.distributed._symmetric_memory's
+    (plumbing); what this package adds is the kernel that stores through `multicast_ptr` (pg_hgemm_mcast).
+    `local` is this rank's copy.  Raises if the group's GPUs offer no multicast (no NVSwitch).  Keep every rank
+    alive until close(): a rank must not exit while its memory is bound and peers still store.
+    """
+
+    def __init__(self, rows: int, cols: int, dtype: torch.dtype, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        assert dist.is_initialized(), "MulticastMatrix needs torch.distributed"
+        assert dtype in (torch.bfloat16, torch.float16)
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank = dist.get_rank(self.group)
+        self.world = dist.get_world_size(self.group)
+        self.rows, self.cols, self.dtype = rows, cols, dtype
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.local = symm_mem.empty(rows, cols, dtype=dtype, device=dev)
+        self._handle = symm_mem.rendezvous(self.local, self.group)
+        self.multicast_ptr = int(self._handle.multicast_ptr)
+        if self.multicast_ptr == 0:
+            raise RuntimeError("this group's GPUs offer no NVLink multicast (NVLS): use PeerMatrix / gathered_fused")
+        dist.barrier(group=self.group)
+
+    def close(self) -> None:
+        """Collective: every rank's kernels have completed before any rank lets go of the memory."""
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        self._handle = None
+        self.local = None
+        dist.barrier(group=self.group)
+
+
 def _default_gemm(c, a, b, ldc, max_sms):
     from . import capi   # the CUDA path; there is no fallback
 
@@ -165,6 +201,22 @@ class ShardedGemm:
             order = [self.rank] + [r for r in range(self.world) if r != self.rank]
             ptrs = [c.block_ptr(r, self.start) for r in order]
             capi.hgemm_multi(ptrs, a, b_shard, ldc=self.n, max_sms=max_sms)
+        if self.world > 1:
+            dist.barrier(group=self.group)      # NCCL: ordered on the stream behind this rank's GEMM
+        return c.local
+
+    def gathered_multicast(self, c: "MulticastMatrix", a: torch.Tensor, b_shard: torch.Tensor,
+                           max_sms: int = 0) -> torch.Tensor:
+        """Replicated row-major C[m, n] with the gather done by the NVLink switch: ONE kernel per rank whose epilogue
+        writes this rank's column block through the multicast address of `c` (pg_hgemm_mcast, multimem.st), so each
+        output byte leaves the GPU once and the switch delivers it to every rank's copy.  A stream-ordered barrier
+        closes the step.  Returns this rank's copy."""
+        from . import capi
+
+        assert (c.rows, c.cols) == (a.shape[0], self.n) and c.world == self.world and c.dtype == a.dtype
+        if self.n_local:
+            capi.hgemm_mcast(c.local.data_ptr() + 2 * self.start, c.multicast_ptr + 2 * self.start, a, b_shard,
+                             ldc=self.n, max_sms=max_sms)
         if self.world > 1:
             dist.barrier(group=self.group)      # NCCL: ordered on the stream behind this rank's GEMM
         return c.local

@@ -20,7 +20,7 @@ def declared_functions():
 
 def test_header_declares_the_expected_surface():
     names = declared_functions()
-    for must in ("pg_hgemm", "pg_hgemm_ex", "pg_hgemm_ws", "pg_hgemm_workspace_bytes", "pg_hgemm_fused", "pg_rmsnorm_rstd", "pg_hgemm_multi", "pg_sgemm", "pg_hgemm_config", "pg_rmsnorm_fwd", "pg_rmsnorm_bwd",
+    for must in ("pg_hgemm", "pg_hgemm_ex", "pg_hgemm_ws", "pg_hgemm_workspace_bytes", "pg_hgemm_fused", "pg_rmsnorm_rstd", "pg_hgemm_multi", "pg_hgemm_mcast", "pg_sgemm", "pg_hgemm_config", "pg_rmsnorm_fwd", "pg_rmsnorm_bwd",
                  "pg_rmsnorm_bwd_workspace_bytes", "pg_rmsnorm_bwd_static", "pg_device_status",
                  "pg_status_string", "pg_last_cuda_error", "pg_version", "pg_peer_alloc", "pg_peer_open",
                  "pg_peer_close", "pg_peer_free", "pg_probe_tensor_peak", "pg_probe_copy"):

@@ -151,6 +151,60 @@ def _worker_benchmark_tiling(rank, world, port, errors):
         raise
 
 
+def _worker_multicast(rank, world, port, errors):
+    """The gather done by the NVLink switch: every rank's block written through the multicast address
+    (pg_hgemm_mcast) must give, on every rank, the same bits as the NCCL gather; at a shape of the one-CTA / CTA-pair
+    kernels and at one whose per-rank block takes the 512 x 256 kernel.  Every rank stays until the matrix is closed."""
+    try:
+        sys.path.insert(0, REPO)
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        import torch.distributed as dist
+
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        import oracle
+        from peakgemm_b200 import capi
+        from peakgemm_b200.dist import MulticastMatrix, ShardedGemm
+        from tests import helpers
+
+        for (m, n_per, k) in ((1536, 1024, 512), (8192, 2304, 1024), (300, 264, 136)):
+            n = n_per * world
+            a, b = oracle.gemm_inputs_uniform(m, n, k, torch.bfloat16, 4)
+            sg = ShardedGemm(n)
+            ad, bd = a.cuda(), b[sg.start:sg.stop].contiguous().cuda()
+            got = sg.gathered(ad, bd, layout="row_major")
+            torch.cuda.synchronize()
+            rows = torch.arange(min(m, 16)) * max(1, m // 16)
+            helpers.check_gemm(got[rows.cuda()], a[rows], b, exact_rows=False)
+            try:
+                mm = MulticastMatrix(m, n, torch.bfloat16)
+            except RuntimeError as e:          # no NVSwitch multicast on this machine: nothing to test
+                if "multicast" in str(e):
+                    break
+                raise
+            mm.local.fill_(float("nan"))
+            torch.cuda.synchronize()
+            dist.barrier()
+            out = sg.gathered_multicast(mm, ad, bd)
+            torch.cuda.synchronize()
+            dist.barrier()
+            assert torch.equal(out, got), "multicast gather differs from the NCCL gather"
+            assert capi.device_status() == 0
+            mm.close()
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as e:  # noqa: BLE001
+        errors.put(f"rank {rank}: {e!r}")
+        raise
+
+
+def test_sharded_gemm_multicast_store(cuda):
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs")
+    _run_gpu_ranks(_worker_multicast, world)
+
+
 def test_sharded_gemm_benchmark_tiling(cuda):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs at least 2 GPUs")

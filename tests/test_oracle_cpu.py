@@ -150,3 +150,25 @@ def test_input_generators_are_seeded():
     assert b1.float().std() < 0.03 and 0.8 < a1.float().std() < 1.2
     x, dy, g = oracle.rmsnorm_inputs(8, 64, torch.bfloat16, 3)
     assert g.dtype == torch.float32 and abs(float(g.mean()) - 1.0) < 0.1 and not torch.equal(x, dy)
+
+
+def test_checker_rejects_a_truncating_epilogue_and_a_lost_product():
+    """The per-element check of tests/helpers.py:check_gemm is not vacuous: a correctly rounded product passes, the
+    same sums truncated toward zero fail, and so does a product with ONE term of every sum dropped, although both stay
+    inside the global acceptance bound."""
+    from tests import helpers
+
+    a, b = oracle.gemm_inputs_uniform(96, 80, 2048, torch.bfloat16, 0)
+    acc = oracle.gemm_exact_acc(a, b)
+    helpers.check_gemm(oracle.gemm_fp32(a, b).to(torch.bfloat16), a, b, exact_rows=True)
+    truncated = (acc.view(torch.int32) & ~0xFFFF).view(torch.float32).to(torch.bfloat16)
+    tol = oracle.gemm_tolerance(2048, acc)
+    assert (truncated.float() - acc).abs().max().item() <= tol          # the loose bound alone would accept it
+    with pytest.raises(AssertionError):
+        helpers.check_gemm(truncated, a, b, exact_rows=True)
+    a_lost = a.clone()
+    a_lost[:, 17] = 0                                                       # one product of 2048 missing per element
+    lost = oracle.gemm_fp32(a_lost, b).to(torch.bfloat16)
+    assert (lost.float() - acc).abs().max().item() <= tol
+    with pytest.raises(AssertionError):
+        helpers.check_gemm(lost, a, b, exact_rows=True)
