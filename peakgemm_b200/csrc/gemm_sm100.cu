@@ -184,6 +184,9 @@ struct EpiArgs {
                                 // thread that produces it, before that thread hands it to the store)
     uint32_t ldr;
     uint32_t pdl_wait;          // non-zero: griddepcontrol.wait before the first read of row_scale
+    uint32_t pdl_all;           // non-zero (split-K and skinny kernels; the persistent kernel has kFlagPdl): launched
+                                // under programmatic stream serialisation: let the successor start after set-up, touch
+                                // no global memory before the predecessor has completed
     // Non-null: the output goes out through this address instead of the TMA stores.  It is a MULTICAST address
     // (one mapping bound to a buffer on every GPU of the group): each 16-byte multimem.st is replicated by the
     // NVLink switch into every GPU's copy, the issuing GPU's own included, so a column-sharded caller's block
@@ -983,9 +986,11 @@ hgemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     cluster_wait();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot_gen;
+    if (epi.pdl_all) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0) {
         if (lane == 0) {
+            if (epi.pdl_all) asm volatile("griddepcontrol.wait;" ::: "memory");
             uint32_t stage = 0, phase = 0;
             // the weights pass through once (evict first); the activations are what every CTA re-reads (evict last)
             const uint64_t pol_stream = l2_policy_evict_first(), pol_keep = l2_policy_evict_last();
@@ -1064,6 +1069,7 @@ hgemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 
     if (warp >= 2) {
         // ===== reduce my W columns and store them =====
+        if (epi.pdl_all) asm volatile("griddepcontrol.wait;" ::: "memory");
         const uint32_t q = warp & 3u;
         const uint32_t row = q * 32u + lane;
         const uint32_t grow = mi * kBM + row;
@@ -1194,9 +1200,11 @@ hgemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_con
     }
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot_gen;
+    if (epi.pdl_all) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0) {
         if (lane == 0) {
+            if (epi.pdl_all) asm volatile("griddepcontrol.wait;" ::: "memory");
             uint32_t stage = 0, phase = 0;
             // the weights pass through once (evict first); the activations are what every CTA re-reads (evict last)
             const uint64_t pol_stream = l2_policy_evict_first(), pol_keep = l2_policy_evict_last();
@@ -1272,6 +1280,7 @@ hgemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_con
             cluster_wait();
         }
         if (owner == rank) {
+            if (epi.pdl_all) asm volatile("griddepcontrol.wait;" ::: "memory");
             const float *recv = reinterpret_cast<const float *>(smem_gen + C::kOffRecv);
             for (uint32_t r2 = 0; r2 < S; ++r2) {
                 if (r2 == rank) continue;
@@ -1455,6 +1464,12 @@ cudaError_t device_info(DeviceInfo **out) {
     return cudaSuccess;
 }
 
+// Ordinary launches go out under programmatic stream serialisation (PEAKGEMM_TUNE_PDL=0 in a tuning build: off).
+bool pdl_enabled() {
+    static const int env_pdl = tune_env_int("PEAKGEMM_TUNE_PDL", 1);
+    return env_pdl != 0;
+}
+
 EpiArgs make_epi(const GemmArgs &g) {
     EpiArgs e;
     e.row_scale = g.row_scale;
@@ -1462,6 +1477,7 @@ EpiArgs make_epi(const GemmArgs &g) {
     e.residual = static_cast<const uint16_t *>(g.residual);
     e.ldr = static_cast<uint32_t>(g.ldr);
     e.pdl_wait = (g.pdl_wait && g.row_scale) ? 1u : 0u;
+    e.pdl_all = (!e.pdl_wait && pdl_enabled()) ? 1u : 0u;
     e.mc_dst = static_cast<uint16_t *>(g.mc_dst);
     e.ld_mc = static_cast<uint32_t>(g.ldc);
     return e;
@@ -1475,7 +1491,7 @@ int fill_attrs(cudaLaunchAttribute *attr, unsigned cluster_x, const GemmArgs &g)
     attr[0].val.clusterDim.x = cluster_x;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
-    if (!(g.pdl_wait && g.row_scale)) return 1;
+    if (!(g.pdl_wait && g.row_scale) && !pdl_enabled()) return 1;
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     return 2;
@@ -1594,7 +1610,9 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
     // reads of the second shape 8.9-12.4 -> 6.4 GB, requests merged on the way to L2 x 3-5).
     // PEAKGEMM_TUNE_WAVESYNC (builds with PG_ENABLE_TUNING only): 0 off, 1 on, -1 automatic.
     static const int env_wave = tune_env_int("PEAKGEMM_TUNE_WAVESYNC", -1);
-    const bool wave_auto = tiles >= 2 * workers && g.k >= 2048 &&
+    // Only with two row blocks per CTA (k-blocks of 1024 tensor-pipe cycles, 4 stages): the 256 x 256 pair kernel lost
+    // with the same scheme (4096 x 14336 x 4096: 314 -> 362 us).
+    const bool wave_auto = MT == 2 && tiles >= 2 * workers && g.k >= 2048 &&
                            static_cast<double>(g.m) * static_cast<double>(g.n) * static_cast<double>(g.k) >= 1.0e11;
     if ((env_wave > 0 || (env_wave < 0 && wave_auto)) && tail.split < 2 && tiles > workers && d.wave_sync) {
         static std::atomic<unsigned> slot_counter{0};
@@ -1607,6 +1625,9 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
     if (tail.split >= 2) {
         // Owners wait for helper CTAs of the same grid: ask for a cooperative launch, which starts the grid only
         // when all of it can be resident at once.  If the device refuses, run without the split.
+        // (without the programmatic-serialisation attribute: this launch neither triggers nor waits)
+        const unsigned attrs_before = cfg.numAttrs;
+        if (!(g.pdl_wait && g.row_scale)) cfg.numAttrs = 1;
         attr[cfg.numAttrs].id = cudaLaunchAttributeCooperative;
         attr[cfg.numAttrs].val.cooperative = 1;
         ++cfg.numAttrs;
@@ -1615,19 +1636,14 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
                                                  flags, make_epi(g), tail, d.status_word);
         if (e == cudaSuccess) return e;
         cudaGetLastError();
-        --cfg.numAttrs;
+        cfg.numAttrs = fill_attrs(attr, CTA_GROUP, g);
+        (void)attrs_before;
         tail = TailArgs{static_cast<uint32_t>(tiles), 0u, nullptr, nullptr, nullptr, 0u, 0u};
     }
     // An ordinary (not cooperative) launch goes out under programmatic stream serialisation, see kFlagPdl.  Not
     // when the caller chained this GEMM behind the kernel that produces row_scale: that mode has its own, later wait.
     uint32_t launch_flags = flags;
-    static const int env_pdl = tune_env_int("PEAKGEMM_TUNE_PDL", 1);
-    if (env_pdl && !(g.pdl_wait && g.row_scale)) {
-        attr[cfg.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[cfg.numAttrs].val.programmaticStreamSerializationAllowed = 1;
-        ++cfg.numAttrs;
-        launch_flags |= kFlagPdl;
-    }
+    if (pdl_enabled() && !(g.pdl_wait && g.row_scale)) launch_flags |= kFlagPdl;    // fill_attrs set the attribute
     return cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b, tm_c, n_dst, static_cast<uint32_t>(g.m),
                               static_cast<uint32_t>(g.n), static_cast<uint32_t>(g.k), group_m, launch_flags,
                               make_epi(g), tail, d.status_word);
