@@ -570,9 +570,9 @@ def config5_block(world: int, rank: int, steps: int = 3) -> dict:
         res["nccl_gather_shard_major_ms"] = timed(
             lambda: sg.gathered(a, b, layout="shard_major", bands=4, max_sms=140), steps)
         res["nccl_gather_ms"] = timed(lambda: sg.gathered(a, b, layout="row_major", bands=4, max_sms=140), steps)
+        nccl = sg.gathered(a, b, layout="row_major", bands=4, max_sms=140)
         pm = PeerMatrix(m, n, torch.bfloat16)
         res["fused_gather_ms"] = timed(lambda: sg.gathered_fused(pm, a, b), steps)
-        nccl = sg.gathered(a, b, layout="row_major", bands=4, max_sms=140)
         fused = sg.gathered_fused(pm, a, b)
         torch.cuda.synchronize()
         same = torch.equal(fused, nccl)
@@ -584,8 +584,9 @@ def config5_block(world: int, rank: int, steps: int = 3) -> dict:
 
         try:
             mm = MulticastMatrix(m, n, torch.bfloat16)
-        except RuntimeError:
+        except RuntimeError as exc:              # raised on every rank or on none (the constructor agrees first)
             mm = None
+            res["multicast_unavailable"] = str(exc)[:200]
         if mm is not None:
             res["multicast_gather_ms"] = timed(lambda: sg.gathered_multicast(mm, a, b), steps)
             mc = sg.gathered_multicast(mm, a, b)

@@ -272,9 +272,11 @@ __global__ void __launch_bounds__(1024)
 rmsnorm_dgamma_reduce_kernel(float *__restrict__ dgamma, const float *partial, int nparts, int h4) {
     __shared__ float4 red[32][33];
     // Launched with programmatic stream serialization: this grid may be scheduled while the backward kernel
-    // is still draining; nothing of its output is touched before the dependency has fully completed.  `partial`
+    // is still draining; nothing of its output is touched before the dependency has fully completed; and it lets
+    // its own successor in the stream be launched at once (that kernel orders itself the same way).  `partial`
     // is written by that kernel AFTER this grid may have started, so it is not read-only for this grid's
     // lifetime: plain L2 loads (ld.global.cg), never the read-only path.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int cx = threadIdx.x & 31, sl = threadIdx.x >> 5;
     const int col = blockIdx.x * 32 + cx;

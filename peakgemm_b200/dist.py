@@ -131,12 +131,27 @@ class MulticastMatrix:
         self.world = dist.get_world_size(self.group)
         self.rows, self.cols, self.dtype = rows, cols, dtype
         dev = torch.device("cuda", torch.cuda.current_device())
-        self.local = symm_mem.empty(rows, cols, dtype=dtype, device=dev)
+        # The constructor is collective.  Each step that can fail on one rank alone is followed by an agreement, so
+        # that either every rank goes on or every rank raises: nobody is left waiting in a rendezvous.
+        self.local, err = None, ""
+        try:
+            self.local = symm_mem.empty(rows, cols, dtype=dtype, device=dev)
+        except Exception as exc:  # noqa: BLE001  (allocation failure of any kind: the ranks must agree on it)
+            err = repr(exc)
+        self._agree(self.local is not None, f"symmetric allocation failed on a rank ({err})")
         self._handle = symm_mem.rendezvous(self.local, self.group)
         self.multicast_ptr = int(self._handle.multicast_ptr)
-        if self.multicast_ptr == 0:
-            raise RuntimeError("this group's GPUs offer no NVLink multicast (NVLS): use PeerMatrix / gathered_fused")
+        self._agree(self.multicast_ptr != 0,
+                    "this group's GPUs offer no NVLink multicast (NVLS): use PeerMatrix / gathered_fused")
         dist.barrier(group=self.group)
+
+    def _agree(self, ok: bool, message: str) -> None:
+        flag = torch.tensor([int(ok)], device=torch.device("cuda", torch.cuda.current_device()))
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        if int(flag.item()) == 0:
+            self.local = None
+            self._handle = None
+            raise RuntimeError("multicast matrix: " + message)
 
     def close(self) -> None:
         """Collective: every rank's kernels have completed before any rank lets go of the memory."""
