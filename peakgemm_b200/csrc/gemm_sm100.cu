@@ -319,7 +319,6 @@ struct TailArgs {
     uint32_t *wave_sync;    // null, or a zeroed pair {arrivals, workers checked out}: the producers keep in step
     uint32_t sync_kb;       // k-blocks between two synchronisation points inside a tile (0: only at the tile's start)
     uint32_t sync_lag;      // the wait for a point comes this many k-blocks after the arrival at it
-    uint32_t sync_slack;    // a wait is over when all but this many workers have arrived (stragglers hold nobody up)
 };
 
 struct Unit {
@@ -515,8 +514,8 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                             sync_target += min(workers, total_tiles - it * workers);
                             sync_wait_at = kb + tail.sync_lag;
                         }
-                        if (kb == sync_wait_at && sync_waits)
-                            sync_waits = wait_count_patiently(tail.wave_sync, sync_target - tail.sync_slack);
+                        // (letting a wait end when all but 4-37 workers had arrived was measured: no gain)
+                        if (kb == sync_wait_at && sync_waits) sync_waits = wait_count_patiently(tail.wave_sync, sync_target);
                     }
                     if (leader) {
                         // wait until the MMAs that read this stage have completed
@@ -1571,7 +1570,7 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
     const uint64_t tiles = m_tiles * n_tiles;
     uint64_t workers = static_cast<uint64_t>(sms / CTA_GROUP);
 
-    TailArgs tail = {static_cast<uint32_t>(tiles), 0u, nullptr, nullptr, nullptr, 0u, 0u, 0u};
+    TailArgs tail = {static_cast<uint32_t>(tiles), 0u, nullptr, nullptr, nullptr, 0u, 0u};
     if (CTA_GROUP == 2 && BN == 256 && MT == 1 && g.workspace && g.n_extra_dst == 0 && !g.mc_dst) {
         uint32_t full = 0, split = 0;
         size_t need = 0;
@@ -1623,8 +1622,6 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
         tail.sync_kb = static_cast<uint32_t>(env_sync_kb);
         static const int env_sync_lag = tune_env_int("PEAKGEMM_TUNE_SYNC_LAG", 1);
         tail.sync_lag = static_cast<uint32_t>(env_sync_lag);
-        static const int env_sync_slack = tune_env_int("PEAKGEMM_TUNE_SYNC_SLACK", 0);
-        tail.sync_slack = static_cast<uint32_t>(env_sync_slack) < workers ? static_cast<uint32_t>(env_sync_slack) : 0u;
     }
     if (tail.split >= 2) {
         // Owners wait for helper CTAs of the same grid: ask for a cooperative launch, which starts the grid only
@@ -1642,7 +1639,7 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
         cudaGetLastError();
         cfg.numAttrs = fill_attrs(attr, CTA_GROUP, g);
         (void)attrs_before;
-        tail = TailArgs{static_cast<uint32_t>(tiles), 0u, nullptr, nullptr, nullptr, 0u, 0u, 0u};
+        tail = TailArgs{static_cast<uint32_t>(tiles), 0u, nullptr, nullptr, nullptr, 0u, 0u};
     }
     // An ordinary (not cooperative) launch goes out under programmatic stream serialisation, see kFlagPdl.  Not
     // when the caller chained this GEMM behind the kernel that produces row_scale: that mode has its own, later wait.
