@@ -1764,7 +1764,10 @@ void choose_config(const GemmArgs &g, int sm_count, int *variant, int *block_n) 
         const int64_t tiles = ((g.m + 511) / 512) * ((g.n + 255) / 256);
         const int64_t workers = sm_count / 2;
         const int64_t waves = (tiles + workers - 1) / workers;
-        const double cost = static_cast<double>(waves) * 512.0 / (1.06 * 1.05);
+        // the 5 % only show over several waves; one or two waves of large tiles run no faster per flop than the
+        // 256 x 256 tile, which then wins the tie (512 x 14336 x 4096: 48.8 against 51.3 us, 2048 x 4096 x 4096: 48.2
+        // against 50.3)
+        const double cost = static_cast<double>(waves) * 512.0 / (1.06 * (waves >= 3 ? 1.05 : 1.0));
         if (cost < best) { best = cost; best_v = 5; best_bn = 256; }
     }
     *variant = best_v;
@@ -1876,10 +1879,10 @@ int hgemm_launch(const GemmArgs &g, int variant, int block_n, int max_sms, cudaS
             if (use) { sk_bn = bn; sk_s = sp; }
             else { variant = 1; block_n = bn; }
         } else if (use && variant == 0) {
-            int v1 = 1, b1 = 0;
-            choose_config(g, sms, &v1, &b1);
-            const int64_t tiles1 = ((g.m + 127) / 128) * ((g.n + b1 - 1) / b1);
-            use = env_split != 0 && g.m <= 256 && tiles1 * 10 < static_cast<int64_t>(sms) * 6;
+            // Two tile rows (128 < m <= 256): a cluster over k wherever a plan exists and k is long enough to
+            // share out (256 x 4096 x 4096: 17.9 us against 21.5-22.4 for the best one-CTA and CTA-pair
+            // configurations, cuBLAS 16.4).
+            use = env_split != 0 && g.m <= 256 && g.k >= 2048;
         }
         if (variant == 3 && !use) return kLaunchBadConfig;
         if (use) {

@@ -106,8 +106,9 @@ def test_config_choice_is_host_arithmetic():
     assert capi.hgemm_config(32768, 4096, 16384) == (5, 256)      # one rank's block of the sharded benchmark shape
     assert capi.hgemm_config(2048, 2048, 2048) == (2, 256)        # 32 large tiles would idle most SM pairs
     assert capi.hgemm_config(4096, 14336, 4096) == (2, 256)       # 448 large tiles: 7 waves for 6.05 waves of work
-    assert capi.hgemm_config(4096, 4096, 256) == (5, 256)         # the shapes tests/test_fused_gpu.py relies on
-    assert capi.hgemm_config(4000, 4104, 136) == (5, 256)
+    assert capi.hgemm_config(4096, 4096, 4096) == (2, 256)        # two waves of large tiles: no gain, the tie goes to 256 x 256
+    assert capi.hgemm_config(8192, 3328, 256) == (5, 256)         # the shapes tests/test_fused_gpu.py and
+    assert capi.hgemm_config(8000, 3304, 136) == (5, 256)         # tests/test_dist_gpu.py rely on: 208 large tiles, 3 waves
     v, bn = capi.hgemm_config(16, 4096, 4096)
     assert v == 1 and bn == 64                                    # one tile row: no pair, most CTAs
     v, bn = capi.hgemm_config(128, 128256, 4096)

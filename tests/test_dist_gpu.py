@@ -121,7 +121,7 @@ def _worker_benchmark_tiling(rank, world, port, errors):
         from tests import helpers
 
         m, k = 8192, 1024
-        n = 2304 * world                  # 16 x 9 = 144 large tiles per rank: 1.95 waves on 74 SM pairs
+        n = 3328 * world                  # 16 x 13 = 208 large tiles per rank: 2.8 waves on 74 SM pairs
         a, b = oracle.gemm_inputs_uniform(m, n, k, torch.bfloat16, 4)
         sg = ShardedGemm(n)
         assert capi.hgemm_config(m, sg.n_local, k) == (5, 256)
@@ -167,7 +167,7 @@ def _worker_multicast(rank, world, port, errors):
         from peakgemm_b200.dist import MulticastMatrix, ShardedGemm
         from tests import helpers
 
-        for (m, n_per, k) in ((1536, 1024, 512), (8192, 2304, 1024), (300, 264, 136)):
+        for (m, n_per, k) in ((1536, 1024, 512), (8192, 3328, 1024), (300, 264, 136)):
             n = n_per * world
             a, b = oracle.gemm_inputs_uniform(m, n, k, torch.bfloat16, 4)
             sg = ShardedGemm(n)

@@ -29,8 +29,8 @@ SHAPES = [
     pytest.param(128, 14336, 1024, id="one-cta"),
     pytest.param(1024, 4096, 1024, id="pair"),
     pytest.param(300, 456, 264, id="pair-tails"),
-    pytest.param(4096, 4096, 256, id="pair-two-row-blocks"),
-    pytest.param(4000, 4104, 136, id="pair-two-row-blocks-tails"),
+    pytest.param(8192, 3328, 256, id="pair-two-row-blocks"),
+    pytest.param(8000, 3304, 136, id="pair-two-row-blocks-tails"),
 ]
 
 

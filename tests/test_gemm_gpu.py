@@ -238,6 +238,20 @@ def test_multi_destination_epilogue(cuda):
     helpers.check_gemm(outs3[0], a3, b3, exact_rows=False)
     for o in outs3:
         assert torch.equal(o, single)
+    # a shape of the 512 x 256 kernel (208 large tiles, three waves), tails in m and n
+    m5, n5, k5 = 8000, 3304, 136
+    assert capi.hgemm_config(m5, n5, k5) == (5, 256)
+    a5, b5 = oracle.gemm_inputs_uniform(m5, n5, k5, BF16, 15)
+    outs5 = [helpers.garbage_like((m5, n5), BF16, "cuda") for _ in range(3)]
+    capi.hgemm_multi([o.data_ptr() for o in outs5], a5.cuda(), b5.cuda(), ldc=n5)
+    single5 = helpers.garbage_like((m5, n5), BF16, "cuda")
+    capi.hgemm(single5, a5.cuda(), b5.cuda())
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0
+    rows5 = torch.arange(64) * 125
+    helpers.check_gemm(outs5[0][rows5.cuda()], a5[rows5], b5, exact_rows=False)
+    for o in outs5:
+        assert torch.equal(o, single5)
     # a small-m case takes the one-CTA kernel
     a2, b2 = oracle.gemm_inputs_uniform(48, 256, 512, F16, 13)
     outs = [helpers.garbage_like((48, 256), F16, "cuda") for _ in range(2)]
