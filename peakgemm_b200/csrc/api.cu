@@ -66,7 +66,7 @@ int pg_hgemm_ex(void *c, const void *a, const void *b, int64_t m, int64_t n, int
                 int64_t ldb, int64_t ldc, int dtype, int variant, int block_n, int max_sms, void *stream) {
     if (m < 0 || n < 0 || k < 0 || max_sms < 0) return PG_ERR_BAD_ARG;
     if (dtype != PG_F16 && dtype != PG_BF16) return PG_ERR_BAD_ARG;
-    if (variant < 0 || variant > 5) return PG_ERR_BAD_ARG;
+    if (variant < 0 || variant > 6) return PG_ERR_BAD_ARG;
     if (block_n != 0 && block_n != 64 && block_n != 128 && block_n != 256) return PG_ERR_BAD_ARG;
     if (m == 0 || n == 0) return PG_OK;
     if (!c || (k > 0 && (!a || !b))) return PG_ERR_BAD_ARG;

@@ -90,6 +90,45 @@ def test_pair_two_row_blocks_matches_pair_kernel_bitwise(cuda):
                                   0, None) == 1      # variant 5 exists at block_n 256 only
 
 
+# ---- pair split-K (variant 6, 64 < m <= 128): a CTA pair per 128 x 256 or 128 x 128 tile (2-CTA MMA at M = 128, 64 rows
+# of A per CTA), 1 or 2 pairs over k per cluster, partial sums through distributed shared memory
+@pytest.mark.parametrize("dtype", [BF16, F16])
+@pytest.mark.parametrize("m,n,k,block_n", [
+    (128, 256, 64, 256),      # one tile, one k-block: one pair
+    (128, 256, 4096, 256),    # one tile, 2 pairs over k
+    (128, 256, 4096, 128),    # two 128-wide tiles, 2 pairs each
+    (128, 4096, 4096, 0),     # benchmark config 3 shape: automatic width and pairs
+    (128, 8192, 2048, 0),
+    (128, 14336, 1024, 0),    # 56 tiles of 256, one pair each
+    (100, 520, 1000, 256),    # tails in m, n and k; the last k-block ragged
+    (100, 520, 1000, 128),
+    (65, 264, 448, 0),        # 7 k-blocks: too few for 2 pairs; one row in the second CTA
+    (96, 2048, 1152, 256),    # 18 k-blocks over 2 pairs
+    (128, 512, 832, 128),     # 13 k-blocks over 2 pairs: uneven slices
+])
+def test_pair_split_k(cuda, m, n, k, block_n, dtype):
+    run_case(m, n, k, dtype, 6, block_n, seed=24, exact=True)
+
+
+def test_pair_split_k_is_deterministic_and_refuses_other_shapes(cuda):
+    from peakgemm_b200 import capi
+
+    a, b = oracle.gemm_inputs_llm(128, 4096, 14336, BF16, 25)
+    ad, bd = a.cuda(), b.cuda()
+    outs = []
+    for _ in range(3):
+        c = helpers.garbage_like((128, 4096), BF16, "cuda")
+        capi.hgemm(c, ad, bd, variant=6)
+        outs.append(c)
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    helpers.check_gemm(outs[0], a, b, exact_rows=False)
+    p = ad.data_ptr()
+    assert capi.lib().pg_hgemm_ex(p, p, p, 129, 256, 64, 64, 64, 256, 1, 6, 0, 0, None) == 1       # m > 128
+    assert capi.lib().pg_hgemm_ex(p, p, p, 128, 128256, 64, 64, 64, 128256, 1, 6, 0, 0, None) == 1  # too many tiles
+
+
 # ---- cluster split-K (variant 3): 2, 4 or 8 CTAs share a tile and combine partial sums through
 # distributed shared memory.  The shapes steer the planner to every cluster size and slice width.
 @pytest.mark.parametrize("dtype", [BF16, F16])
@@ -560,3 +599,32 @@ def test_tail_split_on_two_streams_with_separate_workspaces(cuda):
     assert capi.device_status() == 0
     helpers.check_gemm(outs[0], a, b, exact_rows=False)
     assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+
+
+def test_synchronised_producers_on_two_streams(cuda):
+    """Two large GEMMs in flight on two streams.  Each takes the 512 x 256 kernel whose producers meet at a counter;
+    with two persistent grids competing for the SMs part of a grid is not resident while the rest already waits at
+    a meeting point.  A wait there has a short patience and no consequence for the result: both launches must finish
+    without a status code and give the bits of a launch that ran alone."""
+    from peakgemm_b200 import capi
+
+    m, n, k = 8192, 8192, 2048
+    assert capi.hgemm_config(m, n, k) == (5, 256)
+    a, b = oracle.gemm_inputs_uniform(m, n, k, BF16, 23)
+    ad, bd = a.cuda(), b.cuda()
+    alone = helpers.garbage_like((m, n), BF16, "cuda")
+    capi.hgemm(alone, ad, bd)
+    torch.cuda.synchronize()
+    rows = torch.arange(32) * 256 + 9
+    helpers.check_gemm(alone[rows.cuda()], a[rows], b, exact_rows=False)
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    outs = [helpers.garbage_like((m, n), BF16, "cuda") for _ in streams]
+    torch.cuda.synchronize()
+    for _ in range(4):
+        for s, o in zip(streams, outs):
+            with torch.cuda.stream(s):
+                capi.hgemm(o, ad, bd, stream=s)
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0
+    for o in outs:
+        assert torch.equal(o.view(torch.int16), alone.view(torch.int16))
