@@ -92,11 +92,12 @@ int pg_hgemm(void *c, const void *a, const void *b,
  *   variant 5 = CTA pair per 512 x 256 tile: two 256-row blocks share every k-block of B
  *               and their two accumulators fill tensor memory (25 % fewer operand bytes
  *               per flop from L2 than variant 2 at block_n 256); block_n 0 or 256
- *   variant 6 = pair split-K for 64 < m <= 128: a CTA pair per 128 x block_n tile (2-CTA MMA at
- *               M = 128: each CTA loads 64 rows of A), 1 or 2 pairs over k per cluster, partial sums
- *               through distributed shared memory; block_n 0, 128 or 256.  Never chosen
- *               automatically (it measured slower than variants 1/3 on every shape tried);
- *               PG_ERR_BAD_ARG if m > 128 or the tiles exceed one wave of CTAs
+ *   variant 6 = pair split-K for problems of few tiles: a CTA pair per 256 x block_n tile (m <= 128:
+ *               per 128 x block_n tile, a 2-CTA MMA at M = 128 in which each CTA loads 64 rows of
+ *               A), 1 or 2 pairs over k per cluster, partial sums through distributed shared
+ *               memory; block_n 0, 128 or 256.  The automatic choice for 128 < m, at most 40
+ *               tiles of 256 x 256 and k >= 6144 (for m <= 128 it measured slower than variants
+ *               1 and 3 and is never chosen); PG_ERR_BAD_ARG if the tiles exceed one wave of CTAs
  *   block_n   = 0 (automatic), 64, 128 or 256
  *   max_sms   = 0 (all SMs), or the number of SMs the persistent grid may occupy;
  *               a caller that overlaps a collective with the GEMM leaves a few

@@ -1127,39 +1127,48 @@ hgemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 // 128 x BN tile two thirds of what an SM pulls from L2 is the SHARED A panel (every tile re-reads all of
 // it).  Here a CTA PAIR owns the 128 x BN tile (tcgen05 cta_group::2 at M = 128): each CTA loads only
 // its own 64 rows of A and BN/2 rows of B, so the A panel crosses from L2 half as often — without any
-// multicast.  A cluster holds S pairs (S = 1, 2 or 4; cluster of 2S CTAs): pair p accumulates k-blocks
-// [p*per, (p+1)*per), and the partial sums are combined through distributed shared memory exactly as
-// in the cluster split-K kernel above, among the S CTAs that hold the same 64 rows.
+// multicast.  A cluster holds S pairs (S = 1 or 2; cluster of 2S CTAs): pair p accumulates k-blocks
+// [p*per, (p+1)*per), and the partial sums are combined through distributed shared memory as in the
+// cluster split-K kernel above, between the two CTAs that hold the same rows.
 //
 // Tensor-memory layout of this MMA shape (read out with a one-hot probe): CTA h of the pair holds rows
 // 64h..64h+63 of the tile; lanes 0-63 carry those rows for columns [0, BN/2), lanes 64-127 the same rows
 // for columns [BN/2, BN), both at tensor-memory columns 0..BN/2-1.  So an accumulator takes BN/2 columns,
 // and epilogue warp q (lane quarter q) reads rows 32*(q&1)..+31, column half q>>1.
-template <int BN, int STAGES>
+//
+// ROWS = rows of A per CTA.  64: the shape above (one tile row, 64 < m <= 128).  128: the ordinary M = 256 pair MMA
+// (lane = row, BN tensor-memory columns), for problems of a few 256 x BN tiles (128 < m <= 512 or so) that would
+// leave most SM pairs idle: two pairs per cluster share a tile's k range, with the operand traffic per flop of the
+// 256 x 256 pair tile.  At most two pairs per cluster: a CTA receives from one other pair only, so the receive buffer
+// is half a tile.
+template <int ROWS, int BN, int STAGES>
 struct PsCfg {
-    static constexpr uint32_t kARows = 64;
-    static constexpr uint32_t kABytes = kARows * kBK * 2;          // 8 KiB
+    static constexpr uint32_t kARows = ROWS;
+    static constexpr uint32_t kABytes = kARows * kBK * 2;          // 8 or 16 KiB
     static constexpr uint32_t kBRows = BN / 2;
     static constexpr uint32_t kBBytes = kBRows * kBK * 2;
     static constexpr uint32_t kStageBytes = kABytes + kBBytes;
-    static constexpr uint32_t kTmemCols = BN / 2;
+    static constexpr uint32_t kHalfCols = (ROWS == 64) ? BN / 2 : BN;  // columns one epilogue warp reads = tmem columns
+    static constexpr uint32_t kTmemCols = kHalfCols;
     static constexpr uint32_t kOffA = 0;
     static constexpr uint32_t kOffB = kOffA + STAGES * kABytes;
-    static constexpr uint32_t kOffRecv = kOffB + STAGES * kBBytes;     // [S slots][64 rows][BN/S] fp32
-    static constexpr uint32_t kOffBar = kOffRecv + kARows * BN * 4;    // full[STAGES], empty[STAGES], acc_full
+    static constexpr uint32_t kOffRecv = kOffB + STAGES * kBBytes;     // [ROWS][BN/2] fp32 from the other pair (S = 2)
+    static constexpr uint32_t kOffBar = kOffRecv + kARows * (BN / 2) * 4;   // full[STAGES], empty[STAGES], acc_full
     static constexpr uint32_t kNumBars = 2 * STAGES + 1;
     static constexpr uint32_t kOffMisc = kOffBar + kNumBars * 8;
     static constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;
-    static_assert(kTmemCols == 64 || kTmemCols == 128, "tmem columns");
+    static_assert(kTmemCols == 64 || kTmemCols == 128 || kTmemCols == 256, "tmem columns");
+    static_assert(ROWS == 64 || ROWS == 128, "rows of A per CTA");
     static_assert(kSmemBytes <= 232448, "exceeds 227 KiB of shared memory");
 };
 
-template <int BN, int STAGES, bool BF16>
+template <int ROWS, int BN, int STAGES, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 hgemm_pair_splitk_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                          uint16_t *c, uint32_t ldc, uint32_t M, uint32_t N, uint32_t K, const EpiArgs epi,
                          int *status) {
-    using C = PsCfg<BN, STAGES>;
+    using C = PsCfg<ROWS, BN, STAGES>;
+    constexpr uint32_t HW = C::kHalfCols;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -1167,7 +1176,7 @@ hgemm_pair_splitk_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
     const uint32_t warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t rank = cluster_ctarank();
-    const uint32_t S = cluster_nctarank() / 2;       // pairs per cluster = k-slices
+    const uint32_t S = cluster_nctarank() / 2;       // pairs per cluster = k-slices (1 or 2)
     const uint32_t pair = rank >> 1;                 // k-slice of this CTA's pair
     const uint32_t half = rank & 1u;                 // which 64 rows of A / which BN/2 rows of B this CTA loads
     const bool leader = half == 0;
@@ -1181,7 +1190,9 @@ hgemm_pair_splitk_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
     volatile uint32_t *abort_flag = tmem_slot_gen + 1;
     const WaitCtx ctx{abort_flag, status};
 
-    const uint32_t ni = blockIdx.x / (2 * S);        // one tile row: the tile index is the column block
+    const uint32_t m_tiles = (M + 2 * ROWS - 1) / (2 * ROWS);
+    const uint32_t tile = blockIdx.x / (2 * S);
+    const uint32_t mi = tile % m_tiles, ni = tile / m_tiles;
     const uint32_t k_blocks = (K + kBK - 1) / kBK;
     const uint32_t per = (k_blocks + S - 1) / S;
     const uint32_t kb0 = min(k_blocks, pair * per), kb1 = min(k_blocks, kb0 + per);
@@ -1219,7 +1230,7 @@ hgemm_pair_splitk_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
             uint32_t stage = 0, phase = 0;
             // the weights pass through once (evict first); the activations are what every tile re-reads (evict last)
             const uint64_t pol_stream = l2_policy_evict_first(), pol_keep = l2_policy_evict_last();
-            const int32_t row_a = static_cast<int32_t>(half * C::kARows);
+            const int32_t row_a = static_cast<int32_t>(mi * 2 * ROWS + half * C::kARows);
             const int32_t row_b = static_cast<int32_t>(ni * BN + half * C::kBRows);
             for (uint32_t kb = kb0; kb < kb1; ++kb) {
                 if (leader) {
@@ -1240,8 +1251,8 @@ hgemm_pair_splitk_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
         __syncwarp();
     } else if (warp == 1) {
         if (lane == 0 && leader && has_k) {
-            // ===== MMA issuer (leader CTA of the pair): 128 x BN x 16 per instruction =====
-            constexpr uint32_t idesc = instr_desc_f16(BF16, 128, BN);
+            // ===== MMA issuer (leader CTA of the pair): (2 * ROWS) x BN x 16 per instruction =====
+            constexpr uint32_t idesc = instr_desc_f16(BF16, 2 * ROWS, BN);
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             for (uint32_t kb = kb0; kb < kb1; ++kb) {
@@ -1262,8 +1273,8 @@ hgemm_pair_splitk_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
     } else {
         // ===== send: my partial sums of the columns another pair owns go to that pair's CTA with my rows =====
         const uint32_t q = warp & 3u;
-        const uint32_t row = (q & 1u) * 32u + lane;               // row within this CTA's 64
-        const uint32_t col_half = q >> 1;                          // columns [col_half * BN/2, +BN/2)
+        const uint32_t row = (ROWS == 64 ? (q & 1u) : q) * 32u + lane;   // row within this CTA's ROWS
+        const uint32_t col_half = (ROWS == 64) ? q >> 1 : 0u;            // columns [col_half * HW, +HW)
         bool ok = true;
         if (has_k) {
             ok = wait_bar(bar_acc_full, 0, ctx, kStEpiAccFull);
@@ -1275,7 +1286,7 @@ hgemm_pair_splitk_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
         const uint32_t recv_local = smem_base + C::kOffRecv;
         if (S > 1) {
 #pragma unroll 1
-            for (uint32_t ch = 0; ch < (BN / 2) / 32; ++ch) {
+            for (uint32_t ch = 0; ch < HW / 32; ++ch) {
                 uint32_t v[32];
                 if (has_k && ok) {
                     tmem_ld_32x32b_x32(taddr + ch * 32u, v);
@@ -1286,10 +1297,10 @@ hgemm_pair_splitk_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
                 }
 #pragma unroll
                 for (uint32_t j = 0; j < 8; ++j) {
-                    const uint32_t col = col_half * (BN / 2) + ch * 32u + 4u * j;
+                    const uint32_t col = col_half * HW + ch * 32u + 4u * j;
                     const uint32_t p = col / W;
                     if (p != pair) {
-                        const uint32_t dst = recv_local + ((pair * C::kARows + row) * W + (col - p * W)) * 4u;
+                        const uint32_t dst = recv_local + (row * W + (col - p * W)) * 4u;
                         st_cluster_v4(mapa(dst, 2u * p + half), __uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
                                       __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
                     }
@@ -1308,11 +1319,11 @@ hgemm_pair_splitk_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
         // ===== reduce the columns my pair owns (those of them that lie in this warp's column half) and store =====
         if (epi.pdl_all) asm volatile("griddepcontrol.wait;" ::: "memory");
         const uint32_t q = warp & 3u;
-        const uint32_t row = (q & 1u) * 32u + lane;
-        const uint32_t col_half = q >> 1;
-        const uint32_t grow = half * C::kARows + row;              // m <= 128: one tile row
+        const uint32_t row = (ROWS == 64 ? (q & 1u) : q) * 32u + lane;
+        const uint32_t col_half = (ROWS == 64) ? q >> 1 : 0u;
+        const uint32_t grow = mi * 2 * ROWS + half * C::kARows + row;
         const uint32_t own_lo = pair * W, own_hi = own_lo + W;
-        const uint32_t half_lo = col_half * (BN / 2), half_hi = half_lo + BN / 2;
+        const uint32_t half_lo = col_half * HW, half_hi = half_lo + HW;
         const uint32_t lo = max(own_lo, half_lo), hi = min(own_hi, half_hi);
         const float *recv = reinterpret_cast<const float *>(smem_gen + C::kOffRecv);
         tc_fence_after_sync();
@@ -1332,12 +1343,17 @@ hgemm_pair_splitk_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
             float f[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(o[i]);
-            for (uint32_t r2 = 0; r2 < S; ++r2) {                  // pair order: deterministic
-                if (r2 == pair) continue;
-                const float4 *src = reinterpret_cast<const float4 *>(recv + (r2 * C::kARows + row) * W + (col - own_lo));
+            if (S > 1) {                                           // the other pair's partial sums of my columns
+                const float4 *src = reinterpret_cast<const float4 *>(recv + row * W + (col - own_lo));
                 const float4 a = src[0], b = src[1];
-                f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
-                f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
+                // k order: the pair with the lower k-slice first, whichever side of the sum it is on
+                if (pair == 0) {
+                    f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
+                    f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
+                } else {
+                    f[0] = a.x + f[0]; f[1] = a.y + f[1]; f[2] = a.z + f[2]; f[3] = a.w + f[3];
+                    f[4] = b.x + f[4]; f[5] = b.y + f[5]; f[6] = b.z + f[6]; f[7] = b.w + f[7];
+                }
             }
             const uint32_t gcol = ni * BN + col;
             if (grow < M && gcol < N) {
@@ -1918,10 +1934,10 @@ cudaError_t launch_splitk(const GemmArgs &g, const DeviceInfo &d, int split, cud
                               make_epi(g), d.status_word);
 }
 
-template <int BN, int STAGES, bool BF16>
+template <int ROWS, int BN, int STAGES, bool BF16>
 cudaError_t launch_pair_splitk(const GemmArgs &g, const DeviceInfo &d, int pairs, cudaStream_t stream) {
-    using C = PsCfg<BN, STAGES>;
-    auto kernel = hgemm_pair_splitk_kernel<BN, STAGES, BF16>;
+    using C = PsCfg<ROWS, BN, STAGES>;
+    auto kernel = hgemm_pair_splitk_kernel<ROWS, BN, STAGES, BF16>;
     static DeviceOnce smem_once;
     {
         const cudaError_t e = allow_dynamic_smem(smem_once, kernel, C::kSmemBytes);
@@ -1931,7 +1947,7 @@ cudaError_t launch_pair_splitk(const GemmArgs &g, const DeviceInfo &d, int pairs
     if (!make_tmap(&tm_a, g.a, g.m, g.k, g.lda, C::kARows, BF16, false) ||
         !make_tmap(&tm_b, g.b, g.n, g.k, g.ldb, C::kBRows, BF16, false))
         return cudaErrorInvalidValue;
-    const uint64_t tiles = (g.n + BN - 1) / BN;
+    const uint64_t tiles = ((g.m + 2 * ROWS - 1) / (2 * ROWS)) * ((g.n + BN - 1) / BN);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(tiles * 2 * pairs), 1, 1);
     cfg.blockDim = dim3(kThreads, 1, 1);
@@ -1945,18 +1961,21 @@ cudaError_t launch_pair_splitk(const GemmArgs &g, const DeviceInfo &d, int pairs
                               make_epi(g), d.status_word);
 }
 
-// Tile width (256 or 128) and pairs per cluster (1 or 2) for the pair split-K kernel: the combination with the most
-// CTAs that stays within ~1.1 waves of the SMs, the wider tile on a tie (less operand traffic per flop); every
-// k-slice keeps at least four k-blocks.  pairs = 0: even 256-wide tiles with one pair exceed that (a long n: the
-// persistent kernels take it).  Clusters of 8 CTAs (4 pairs) are left out: 16 of them do not fit the GPU at once
-// (128 x 4096 x 4096 with 4 pairs per cluster: 30 us against 14 us for the same work in clusters of 4).
-void choose_pair_split(const GemmArgs &g, int sm_count, int *bn_out, int *pairs_out) {
+// Tile width (256 or 128) and pairs per cluster (1 or 2) for the pair split-K kernel (tiles of 128 rows for m <= 128,
+// of 256 rows above): the combination with the most CTAs that stays within ~1.1 waves of the SMs, the wider tile on
+// a tie (less operand traffic per flop); every k-slice keeps at least four k-blocks.  pairs = 0: even 256-wide
+// tiles with one pair exceed that (the persistent kernels take such shapes).  Clusters of 8 CTAs (4 pairs) are left
+// out: 16 of them do not fit the GPU at once (128 x 4096 x 4096 with 4 pairs per cluster: 30 us against 16 us for
+// the same work in clusters of 4).
+void choose_pair_split(const GemmArgs &g, int sm_count, int block_n, int *bn_out, int *pairs_out) {
     const int64_t k_blocks = (g.k + 63) / 64;
+    const int64_t m_tiles = g.m <= 128 ? 1 : (g.m + 255) / 256;
     int64_t best_ctas = 0;
     *bn_out = 256;
     *pairs_out = 0;
     for (int bn = 256; bn >= 128; bn /= 2) {
-        const int64_t tiles = (g.n + bn - 1) / bn;
+        if (block_n != 0 && block_n != bn) continue;
+        const int64_t tiles = m_tiles * ((g.n + bn - 1) / bn);
         for (int s = 1; s <= 2; ++s) {
             if (s > 1 && k_blocks < 4 * s) continue;
             const int64_t ctas = tiles * 2 * s;
@@ -1964,6 +1983,24 @@ void choose_pair_split(const GemmArgs &g, int sm_count, int *bn_out, int *pairs_
             if (ctas > best_ctas) { best_ctas = ctas; *bn_out = bn; *pairs_out = s; }
         }
     }
+}
+
+// Whether the automatic choice takes the pair split-K kernel with 256 x 256 tiles and two pairs per tile (asked after
+// the one-CTA cluster split-K kernel, which keeps m <= 256 wherever it has a plan).
+bool pair_split_pays(int64_t m, int64_t n, int64_t k, int sm_count) {
+    if (m <= 128 || k < 6144) return false;
+    const int64_t tiles = ((m + 255) / 256) * ((n + 255) / 256);
+    return tiles * 4 * 10 <= static_cast<int64_t>(sm_count) * 11;
+}
+
+template <int ROWS>
+cudaError_t launch_pair_splitk_any(const GemmArgs &g, const DeviceInfo &d, int bn, int pairs, cudaStream_t stream) {
+    constexpr int kStages256 = ROWS == 64 ? 6 : 5, kStages128 = 8;
+    if (bn == 256)
+        return g.bf16 ? launch_pair_splitk<ROWS, 256, kStages256, true>(g, d, pairs, stream)
+                      : launch_pair_splitk<ROWS, 256, kStages256, false>(g, d, pairs, stream);
+    return g.bf16 ? launch_pair_splitk<ROWS, 128, kStages128, true>(g, d, pairs, stream)
+                  : launch_pair_splitk<ROWS, 128, kStages128, false>(g, d, pairs, stream);
 }
 
 template <int TOK, int STAGES, bool BF16>
@@ -2156,23 +2193,16 @@ int hgemm_launch(const GemmArgs &g, int variant, int block_n, int max_sms, cudaS
         if (e != cudaSuccess) { *cuda_err = e; return kLaunchCuda; }
         return kLaunchOk;
     }
-    // variant 6 = pair split-K (64 < m <= 128): a CTA pair per 128 x 256 tile, 1, 2 or 4 pairs over k per cluster
+    // variant 6 = pair split-K: a CTA pair per 128 x block_n (m <= 128) or 256 x block_n tile, 1 or 2 pairs over k per
+    // cluster; for problems of few tiles
     if (variant == 6) {
-        if (g.m > 128 || staged_store) return kLaunchBadConfig;
+        if (staged_store || (block_n != 0 && block_n != 128 && block_n != 256)) return kLaunchBadConfig;
         int ps_bn = 0, sp = 0;
-        choose_pair_split(g, sms, &ps_bn, &sp);
-        if (block_n == 256 || block_n == 128) {          // the caller fixes the tile width
-            ps_bn = block_n;
-            const int64_t tiles = (g.n + ps_bn - 1) / ps_bn, k_blocks = (g.k + 63) / 64;
-            sp = (tiles * 4 * 10 <= static_cast<int64_t>(sms) * 11 && k_blocks >= 8) ? 2
-                 : (tiles * 2 * 10 <= static_cast<int64_t>(sms) * 11)                ? 1 : 0;
-        }
+        choose_pair_split(g, sms, block_n, &ps_bn, &sp);
         if (sp == 0) return kLaunchBadConfig;
-        if (env_split == 1 || env_split == 2 || env_split == 4) sp = env_split;
-        if (ps_bn == 256) e = g.bf16 ? launch_pair_splitk<256, 6, true>(g, *d, sp, stream)
-                                     : launch_pair_splitk<256, 6, false>(g, *d, sp, stream);
-        else e = g.bf16 ? launch_pair_splitk<128, 8, true>(g, *d, sp, stream)
-                        : launch_pair_splitk<128, 8, false>(g, *d, sp, stream);
+        if (env_split == 1 || (env_split == 2 && (g.k + 63) / 64 >= 8)) sp = env_split;
+        e = g.m <= 128 ? launch_pair_splitk_any<64>(g, *d, ps_bn, sp, stream)
+                       : launch_pair_splitk_any<128>(g, *d, ps_bn, sp, stream);
         if (e != cudaSuccess) { *cuda_err = e; return kLaunchCuda; }
         return kLaunchOk;
     }
@@ -2199,6 +2229,19 @@ int hgemm_launch(const GemmArgs &g, int variant, int block_n, int max_sms, cudaS
                                          : launch_splitk<128, 5, false>(g, *d, sk_s, stream);
             else e = g.bf16 ? launch_splitk<64, 8, true>(g, *d, sk_s, stream)
                             : launch_splitk<64, 8, false>(g, *d, sk_s, stream);
+            if (e != cudaSuccess) { *cuda_err = e; return kLaunchCuda; }
+            return kLaunchOk;
+        }
+    }
+    // Few 256 x 256 tiles and a long k (at most 40 tiles, so that two pairs per tile fit the SMs at once): two CTA
+    // pairs per cluster share each tile's k range and combine through distributed shared memory.  Measured against
+    // the best of the other kernels (us): 512 x 2048 x 8192 27.0 / 31.6, 512 x 4096 x 8192 34.2 / 38.9, 256 x 8192 x
+    // 8192 37.4 / 41.9, 384 x 4096 x 14336 49.8 / 53.2; at k = 4096 it only ties (512 x 4096 x 4096 23.3 / 23.5).
+    if (variant == 0 && block_n == 0 && !staged_store && pair_split_pays(g.m, g.n, g.k, sms)) {
+        int ps_bn = 0, sp = 0;
+        choose_pair_split(g, sms, 0, &ps_bn, &sp);       // 128-wide tiles where 256-wide ones leave SMs idle
+        if (sp == 2) {
+            e = launch_pair_splitk_any<128>(g, *d, ps_bn, sp, stream);
             if (e != cudaSuccess) { *cuda_err = e; return kLaunchCuda; }
             return kLaunchOk;
         }
@@ -2235,6 +2278,7 @@ int hgemm_launch(const GemmArgs &g, int variant, int block_n, int max_sms, cudaS
 // shape; 0 when it would not.
 size_t hgemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int sm_count) {
     if (m <= 256 || k <= 0 || n <= 0) return 0;      // small m: skinny / split-K / one-CTA kernels
+    if (pair_split_pays(m, n, k, sm_count)) return 0;   // two pairs per tile through shared memory: no scratch
     uint32_t full = 0, split = 0;
     size_t bytes = 0;
     plan_tail(m, n, k, sm_count / 2, &full, &split, &bytes);

@@ -105,6 +105,13 @@ def test_pair_two_row_blocks_matches_pair_kernel_bitwise(cuda):
     (65, 264, 448, 0),        # 7 k-blocks: too few for 2 pairs; one row in the second CTA
     (96, 2048, 1152, 256),    # 18 k-blocks over 2 pairs
     (128, 512, 832, 128),     # 13 k-blocks over 2 pairs: uneven slices
+    # 256-row tiles (128 rows of A per CTA, the ordinary M = 256 pair MMA) for m > 128
+    (256, 256, 4096, 256),    # one tile, 2 pairs over k
+    (512, 4096, 4096, 0),     # 32 tiles x 2 pairs
+    (384, 4096, 2048, 0),     # the second tile row half empty
+    (300, 520, 1000, 128),    # tails in m, n and k
+    (512, 2048, 832, 256),    # 13 k-blocks over 2 pairs
+    (129, 264, 64, 0),        # one k-block: one pair; a single row in the second CTA
 ])
 def test_pair_split_k(cuda, m, n, k, block_n, dtype):
     run_case(m, n, k, dtype, 6, block_n, seed=24, exact=True)
@@ -125,8 +132,9 @@ def test_pair_split_k_is_deterministic_and_refuses_other_shapes(cuda):
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
     helpers.check_gemm(outs[0], a, b, exact_rows=False)
     p = ad.data_ptr()
-    assert capi.lib().pg_hgemm_ex(p, p, p, 129, 256, 64, 64, 64, 256, 1, 6, 0, 0, None) == 1       # m > 128
     assert capi.lib().pg_hgemm_ex(p, p, p, 128, 128256, 64, 64, 64, 128256, 1, 6, 0, 0, None) == 1  # too many tiles
+    assert capi.lib().pg_hgemm_ex(p, p, p, 8192, 8192, 64, 64, 64, 8192, 1, 6, 0, 0, None) == 1
+    assert capi.lib().pg_hgemm_ex(p, p, p, 128, 256, 64, 64, 64, 256, 1, 6, 64, 0, None) == 1       # block_n
 
 
 # ---- cluster split-K (variant 3): 2, 4 or 8 CTAs share a tile and combine partial sums through
@@ -487,9 +495,6 @@ def test_roofline_probes(cuda):
     (1024, 14336, 8192),    # remainder 2 -> 4 slices
     (1024, 14336, 16384),   # remainder 2 -> 6 slices
     (1000, 14328, 8256),    # tails in m, n and k
-    (512, 4096, 8192),      # 32 tiles, at most half a wave: every tile is split in 2
-    (512, 4096, 14336),
-    (300, 2056, 8200),      # 18 tiles split in 4, tails in m, n and k
 ])
 def test_tail_split_matches_oracle_and_plain_kernel(cuda, m, n, k, dtype):
     from peakgemm_b200 import capi
@@ -516,9 +521,33 @@ def test_tail_split_matches_oracle_and_plain_kernel(cuda, m, n, k, dtype):
     diff = (split.float() - plain.float()).abs()
     assert diff.max().item() <= 2.0 ** -6 * plain.float().abs().max().item()
     changed = (diff > 0).float().mean().item()
-    all_split = -(-m // 256) * -(-n // 256) * 2 <= 74           # at most half a wave: no whole tiles at all
-    # > 0: the split really ran (its tiles sum in another order); with whole tiles present most of C is untouched
-    assert changed > 0.0 and (all_split or changed < 0.2), changed
+    # > 0: the split really ran (its tiles sum in another order); most of C, the whole tiles, is untouched
+    assert 0.0 < changed < 0.2, changed
+
+
+@pytest.mark.parametrize("m,n,k", [(512, 4096, 8192), (512, 4096, 14336), (300, 2056, 8200), (256, 8192, 8192)])
+def test_few_tiles_and_a_long_k_take_the_pair_split_k_kernel(cuda, m, n, k):
+    """At most 40 tiles of 256 x 256 and k >= 6144: the automatic choice is two CTA pairs per tile sharing k through
+    distributed shared memory (no workspace is asked for); same bits as the explicit variant, and deterministic."""
+    from peakgemm_b200 import capi
+
+    assert capi.hgemm_workspace_bytes(m, n, k) == 0
+    a, b = oracle.gemm_inputs_uniform(m, n, k, BF16, 26)
+    ad, bd = a.cuda(), b.cuda()
+    auto = helpers.garbage_like((m, n), BF16, "cuda")
+    again = helpers.garbage_like((m, n), BF16, "cuda")
+    explicit = helpers.garbage_like((m, n), BF16, "cuda")
+    plain = helpers.garbage_like((m, n), BF16, "cuda")
+    capi.hgemm(auto, ad, bd)
+    capi.hgemm_ws(again, ad, bd, None)
+    capi.hgemm(explicit, ad, bd, variant=6)
+    capi.hgemm(plain, ad, bd, variant=2, block_n=256)
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0
+    helpers.check_gemm(auto, a, b, exact_rows=False)
+    assert torch.equal(auto.view(torch.int16), again.view(torch.int16))
+    assert torch.equal(auto.view(torch.int16), explicit.view(torch.int16))
+    assert not torch.equal(auto.view(torch.int16), plain.view(torch.int16)), "the k range was not split"
 
 
 def test_tail_split_not_offered_where_it_cannot_help(cuda):
