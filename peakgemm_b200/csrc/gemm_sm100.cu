@@ -1081,34 +1081,46 @@ hgemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         const bool fused = epi.any();
         const float rs = fused ? epi_row_scale(epi, grow < M, grow) : 1.f;
 #pragma unroll 1
-        for (uint32_t g = 0; g < W / 8; ++g) {
-            uint32_t o[8];
+        for (uint32_t g0 = 0; g0 < W / 8; g0 += 4) {           // up to 32 columns per round of tensor-memory loads
+            const uint32_t ng = min(4u, W / 8 - g0);
+            uint32_t o[32];
             if (acc_ok) {
-                tmem_ld_32x32b_x8(taddr + 8u * g, o);
+                if (ng == 4) {
+                    tmem_ld_32x32b_x32(taddr + 8u * g0, o);
+                } else {
+                    for (uint32_t gg = 0; gg < ng; ++gg)
+                        tmem_ld_32x32b_x8(taddr + 8u * (g0 + gg), *reinterpret_cast<uint32_t(*)[8]>(&o[8 * gg]));
+                }
                 tmem_ld_wait();
             } else {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) o[i] = 0u;
+                for (int i = 0; i < 32; ++i) o[i] = 0u;
             }
-            float f[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(o[i]);
-            for (uint32_t r2 = 0; r2 < S; ++r2) {
-                if (r2 == rank) continue;
-                const float4 *src = reinterpret_cast<const float4 *>(recv + (r2 * kBM + row) * W + 8u * g);
-                const float4 a = src[0], b = src[1];
-                f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
-                f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
-            }
-            const uint32_t gcol = ni * BN + rank * W + 8u * g;
-            if (grow < M && gcol < N) {
-                if (fused) epi_apply8<BF16>(f, rs, epi, true, grow, gcol);
-                uint4 out;
-                out.x = pack2<BF16>(f[0], f[1]);
-                out.y = pack2<BF16>(f[2], f[3]);
-                out.z = pack2<BF16>(f[4], f[5]);
-                out.w = pack2<BF16>(f[6], f[7]);
-                *reinterpret_cast<uint4 *>(c + static_cast<size_t>(grow) * ldc + gcol) = out;
+            for (uint32_t gg = 0; gg < 4; ++gg) {
+                if (gg < ng) {
+                    const uint32_t g = g0 + gg;
+                    float f[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(o[8 * gg + i]);
+                    for (uint32_t r2 = 0; r2 < S; ++r2) {
+                        if (r2 == rank) continue;
+                        const float4 *src = reinterpret_cast<const float4 *>(recv + (r2 * kBM + row) * W + 8u * g);
+                        const float4 a = src[0], b = src[1];
+                        f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
+                        f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
+                    }
+                    const uint32_t gcol = ni * BN + rank * W + 8u * g;
+                    if (grow < M && gcol < N) {
+                        if (fused) epi_apply8<BF16>(f, rs, epi, true, grow, gcol);
+                        uint4 out;
+                        out.x = pack2<BF16>(f[0], f[1]);
+                        out.y = pack2<BF16>(f[2], f[3]);
+                        out.z = pack2<BF16>(f[4], f[5]);
+                        out.w = pack2<BF16>(f[6], f[7]);
+                        *reinterpret_cast<uint4 *>(c + static_cast<size_t>(grow) * ldc + gcol) = out;
+                    }
+                }
             }
         }
         tc_fence_before_sync();
@@ -1331,39 +1343,43 @@ hgemm_pair_splitk_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
         const bool fused = epi.any();
         const float rs = fused ? epi_row_scale(epi, grow < M, grow) : 1.f;
 #pragma unroll 1
-        for (uint32_t col = lo; col < hi; col += 8) {
-            uint32_t o[8];
+        for (uint32_t col = lo; col < hi; col += 32) {        // 32 columns per round of tensor-memory loads
+            uint32_t o[32];
             if (acc_ok) {
-                tmem_ld_32x32b_x8(tmem_base + ((q * 32u) << 16) + (col - half_lo), o);
+                tmem_ld_32x32b_x32(tmem_base + ((q * 32u) << 16) + (col - half_lo), o);
                 tmem_ld_wait();
             } else {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) o[i] = 0u;
+                for (int i = 0; i < 32; ++i) o[i] = 0u;
             }
-            float f[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(o[i]);
-            if (S > 1) {                                           // the other pair's partial sums of my columns
-                const float4 *src = reinterpret_cast<const float4 *>(recv + row * W + (col - own_lo));
-                const float4 a = src[0], b = src[1];
-                // k order: the pair with the lower k-slice first, whichever side of the sum it is on
-                if (pair == 0) {
-                    f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
-                    f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
-                } else {
-                    f[0] = a.x + f[0]; f[1] = a.y + f[1]; f[2] = a.z + f[2]; f[3] = a.w + f[3];
-                    f[4] = b.x + f[4]; f[5] = b.y + f[5]; f[6] = b.z + f[6]; f[7] = b.w + f[7];
+            for (uint32_t g8 = 0; g8 < 4; ++g8) {
+                float f[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(o[8 * g8 + i]);
+                if (S > 1) {                                       // the other pair's partial sums of my columns
+                    const float4 *src =
+                        reinterpret_cast<const float4 *>(recv + row * W + (col + 8 * g8 - own_lo));
+                    const float4 a = src[0], b = src[1];
+                    // k order: the pair with the lower k-slice first, whichever side of the sum it is on
+                    if (pair == 0) {
+                        f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
+                        f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
+                    } else {
+                        f[0] = a.x + f[0]; f[1] = a.y + f[1]; f[2] = a.z + f[2]; f[3] = a.w + f[3];
+                        f[4] = b.x + f[4]; f[5] = b.y + f[5]; f[6] = b.z + f[6]; f[7] = b.w + f[7];
+                    }
                 }
-            }
-            const uint32_t gcol = ni * BN + col;
-            if (grow < M && gcol < N) {
-                if (fused) epi_apply8<BF16>(f, rs, epi, true, grow, gcol);
-                uint4 out;
-                out.x = pack2<BF16>(f[0], f[1]);
-                out.y = pack2<BF16>(f[2], f[3]);
-                out.z = pack2<BF16>(f[4], f[5]);
-                out.w = pack2<BF16>(f[6], f[7]);
-                *reinterpret_cast<uint4 *>(c + static_cast<size_t>(grow) * ldc + gcol) = out;
+                const uint32_t gcol = ni * BN + col + 8 * g8;
+                if (grow < M && gcol < N) {
+                    if (fused) epi_apply8<BF16>(f, rs, epi, true, grow, gcol);
+                    uint4 out;
+                    out.x = pack2<BF16>(f[0], f[1]);
+                    out.y = pack2<BF16>(f[2], f[3]);
+                    out.z = pack2<BF16>(f[4], f[5]);
+                    out.w = pack2<BF16>(f[6], f[7]);
+                    *reinterpret_cast<uint4 *>(c + static_cast<size_t>(grow) * ldc + gcol) = out;
+                }
             }
         }
         tc_fence_before_sync();
