@@ -96,7 +96,7 @@ int pg_hgemm(void *c, const void *a, const void *b,
  *               per 128 x block_n tile, a 2-CTA MMA at M = 128 in which each CTA loads 64 rows of
  *               A), 1 or 2 pairs over k per cluster, partial sums through distributed shared
  *               memory; block_n 0, 128 or 256.  The automatic choice for 128 < m, at most 40
- *               tiles of 256 x 256 and k >= 6144 (for m <= 128 it measured slower than variants
+ *               tiles of 256 x 256 and k >= 4096 (for m <= 128 it measured slower than variants
  *               1 and 3 and is never chosen); PG_ERR_BAD_ARG if the tiles exceed one wave of CTAs
  *   block_n   = 0 (automatic), 64, 128 or 256
  *   max_sms   = 0 (all SMs), or the number of SMs the persistent grid may occupy;

@@ -926,7 +926,8 @@ struct SkCfg {
     static constexpr uint32_t kTmemCols = BN;
     static constexpr uint32_t kOffA = 0;
     static constexpr uint32_t kOffB = kOffA + STAGES * kABytes;
-    static constexpr uint32_t kOffRecv = kOffB + STAGES * kBBytes;     // [S slots][128 rows][BN/S] fp32
+    static constexpr uint32_t kOffRecv = kOffB + STAGES * kBBytes;     // [S slots][BN/S/4][128 rows][4] fp32: a warp's 32
+                                                                       // rows are 32 consecutive 16-byte words
     static constexpr uint32_t kOffBar = kOffRecv + kBM * BN * 4;       // full[STAGES], empty[STAGES], acc_full
     static constexpr uint32_t kNumBars = 2 * STAGES + 1;
     static constexpr uint32_t kOffMisc = kOffBar + kNumBars * 8;
@@ -1054,7 +1055,7 @@ hgemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 const uint32_t col = ch * 32u + 4u * j;
                 const uint32_t p = col / W;
                 if (p != rank) {
-                    const uint32_t dst = recv_local + ((rank * kBM + row) * W + (col - p * W)) * 4u;
+                    const uint32_t dst = recv_local + ((rank * (W / 4) + ((col - p * W) >> 2)) * kBM + row) * 16u;
                     st_cluster_v4(mapa(dst, p), __uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
                                   __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
                 }
@@ -1105,8 +1106,8 @@ hgemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(o[8 * gg + i]);
                     for (uint32_t r2 = 0; r2 < S; ++r2) {
                         if (r2 == rank) continue;
-                        const float4 *src = reinterpret_cast<const float4 *>(recv + (r2 * kBM + row) * W + 8u * g);
-                        const float4 a = src[0], b = src[1];
+                        const float4 *src = reinterpret_cast<const float4 *>(recv) + (r2 * (W / 4) + 2u * g) * kBM + row;
+                        const float4 a = src[0], b = src[kBM];
                         f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
                         f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
                     }
@@ -1164,7 +1165,7 @@ struct PsCfg {
     static constexpr uint32_t kTmemCols = kHalfCols;
     static constexpr uint32_t kOffA = 0;
     static constexpr uint32_t kOffB = kOffA + STAGES * kABytes;
-    static constexpr uint32_t kOffRecv = kOffB + STAGES * kBBytes;     // [ROWS][BN/2] fp32 from the other pair (S = 2)
+    static constexpr uint32_t kOffRecv = kOffB + STAGES * kBBytes;     // [BN/2/4][ROWS][4] fp32 from the other pair (S = 2)
     static constexpr uint32_t kOffBar = kOffRecv + kARows * (BN / 2) * 4;   // full[STAGES], empty[STAGES], acc_full
     static constexpr uint32_t kNumBars = 2 * STAGES + 1;
     static constexpr uint32_t kOffMisc = kOffBar + kNumBars * 8;
@@ -1299,6 +1300,7 @@ hgemm_pair_splitk_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
         if (S > 1) {
 #pragma unroll 1
             for (uint32_t ch = 0; ch < HW / 32; ++ch) {
+                if ((col_half * HW + ch * 32u) / W == pair) continue;      // my pair keeps these columns
                 uint32_t v[32];
                 if (has_k && ok) {
                     tmem_ld_32x32b_x32(taddr + ch * 32u, v);
@@ -1312,7 +1314,7 @@ hgemm_pair_splitk_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
                     const uint32_t col = col_half * HW + ch * 32u + 4u * j;
                     const uint32_t p = col / W;
                     if (p != pair) {
-                        const uint32_t dst = recv_local + (row * W + (col - p * W)) * 4u;
+                        const uint32_t dst = recv_local + ((((col - p * W) >> 2)) * C::kARows + row) * 16u;
                         st_cluster_v4(mapa(dst, 2u * p + half), __uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
                                       __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
                     }
@@ -1359,8 +1361,8 @@ hgemm_pair_splitk_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
                 for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(o[8 * g8 + i]);
                 if (S > 1) {                                       // the other pair's partial sums of my columns
                     const float4 *src =
-                        reinterpret_cast<const float4 *>(recv + row * W + (col + 8 * g8 - own_lo));
-                    const float4 a = src[0], b = src[1];
+                        reinterpret_cast<const float4 *>(recv) + ((col + 8 * g8 - own_lo) >> 2) * C::kARows + row;
+                    const float4 a = src[0], b = src[C::kARows];
                     // k order: the pair with the lower k-slice first, whichever side of the sum it is on
                     if (pair == 0) {
                         f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
@@ -2004,7 +2006,7 @@ void choose_pair_split(const GemmArgs &g, int sm_count, int block_n, int *bn_out
 // Whether the automatic choice takes the pair split-K kernel with 256 x 256 tiles and two pairs per tile (asked after
 // the one-CTA cluster split-K kernel, which keeps m <= 256 wherever it has a plan).
 bool pair_split_pays(int64_t m, int64_t n, int64_t k, int sm_count) {
-    if (m <= 128 || k < 6144) return false;
+    if (m <= 128 || k < 4096) return false;
     const int64_t tiles = ((m + 255) / 256) * ((n + 255) / 256);
     return tiles * 4 * 10 <= static_cast<int64_t>(sm_count) * 11;
 }
@@ -2251,8 +2253,8 @@ int hgemm_launch(const GemmArgs &g, int variant, int block_n, int max_sms, cudaS
     }
     // Few 256 x 256 tiles and a long k (at most 40 tiles, so that two pairs per tile fit the SMs at once): two CTA
     // pairs per cluster share each tile's k range and combine through distributed shared memory.  Measured against
-    // the best of the other kernels (us): 512 x 2048 x 8192 27.0 / 31.6, 512 x 4096 x 8192 34.2 / 38.9, 256 x 8192 x
-    // 8192 37.4 / 41.9, 384 x 4096 x 14336 49.8 / 53.2; at k = 4096 it only ties (512 x 4096 x 4096 23.3 / 23.5).
+    // the best of the other kernels (us): 512 x 2048 x 8192 25.3 / 31.6, 512 x 4096 x 8192 30.2 / 38.9, 256 x 8192 x
+    // 8192 33.9 / 41.9, 384 x 4096 x 14336 47.0 / 53.2, 512 x 4096 x 4096 19.6 / 23.5.
     if (variant == 0 && block_n == 0 && !staged_store && pair_split_pays(g.m, g.n, g.k, sms)) {
         int ps_bn = 0, sp = 0;
         choose_pair_split(g, sms, 0, &ps_bn, &sp);       // 128-wide tiles where 256-wide ones leave SMs idle

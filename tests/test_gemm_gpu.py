@@ -525,9 +525,10 @@ def test_tail_split_matches_oracle_and_plain_kernel(cuda, m, n, k, dtype):
     assert 0.0 < changed < 0.2, changed
 
 
-@pytest.mark.parametrize("m,n,k", [(512, 4096, 8192), (512, 4096, 14336), (300, 2056, 8200), (256, 8192, 8192)])
+@pytest.mark.parametrize("m,n,k", [(512, 4096, 8192), (512, 4096, 14336), (300, 2056, 8200), (256, 8192, 8192),
+                                   (512, 4096, 4096)])
 def test_few_tiles_and_a_long_k_take_the_pair_split_k_kernel(cuda, m, n, k):
-    """At most 40 tiles of 256 x 256 and k >= 6144: the automatic choice is two CTA pairs per tile sharing k through
+    """At most 40 tiles of 256 x 256 and k >= 4096: the automatic choice is two CTA pairs per tile sharing k through
     distributed shared memory (no workspace is asked for); same bits as the explicit variant, and deterministic."""
     from peakgemm_b200 import capi
 
