@@ -2200,8 +2200,17 @@ int hgemm_launch(const GemmArgs &g, int variant, int block_n, int max_sms, cudaS
     static const bool env_no_skinny = tune_env_int("PEAKGEMM_TUNE_SKINNY", 1) == 0;
     if (variant == 4 || (variant == 0 && g.m <= 64 && !env_no_skinny)) {
         if (g.m > 64) return kLaunchBadConfig;
-        int sp = choose_skinny_split(g, sms);
+        static const int env_two = tune_env_int("PEAKGEMM_TUNE_SKINNY_TWO", 0);
+        int sp = choose_skinny_split(g, env_two ? 2 * sms : sms);
         if (variant == 4 && env_split >= 1 && env_split <= 8 && (env_split & (env_split - 1)) == 0) sp = env_split;
+        if (env_two) {
+            if (g.m <= 16) e = g.bf16 ? launch_skinny<16, 5, true>(g, *d, sp, stream)
+                                      : launch_skinny<16, 5, false>(g, *d, sp, stream);
+            else if (g.m <= 32) e = g.bf16 ? launch_skinny<32, 4, true>(g, *d, sp, stream)
+                                           : launch_skinny<32, 4, false>(g, *d, sp, stream);
+            else e = g.bf16 ? launch_skinny<64, 3, true>(g, *d, sp, stream)
+                            : launch_skinny<64, 3, false>(g, *d, sp, stream);
+        } else
         if (g.m <= 16) e = g.bf16 ? launch_skinny<16, 12, true>(g, *d, sp, stream)
                                   : launch_skinny<16, 12, false>(g, *d, sp, stream);
         else if (g.m <= 32) e = g.bf16 ? launch_skinny<32, 10, true>(g, *d, sp, stream)
