@@ -1407,7 +1407,11 @@ hgemm_pair_splitk_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
 // One CTA per 128 weight rows (not persistent); with a cluster of S CTAs each takes a slice of k and
 // the partial tiles are combined through distributed shared memory: CTA r owns 128/S of the tile's
 // rows, every other CTA writes its partial values for those rows into r's receive buffer, one cluster
-// barrier, then r sums in rank order (deterministic) and stores.  S == 1: no exchange.
+// barrier, then r sums in rank order (deterministic) and stores.  S == 1: no exchange, and the launch
+// leaves the receive buffer out of its shared memory.
+// The configurations with few stages (at most 113 KiB per CTA) put TWO CTAs on an SM: one CTA's set-up,
+// first-load latency and epilogue overlap the other's streaming, a launch of more CTAs than SMs loses
+// less to the last wave, and a dependent launch can become resident while its predecessor drains.
 template <int TOK, int STAGES>
 struct SnCfg {
     static constexpr uint32_t kWBytes = kBM * kBK * 2;              // weights tile, 16 KiB
@@ -1416,11 +1420,14 @@ struct SnCfg {
     static constexpr uint32_t kTmemCols = TOK < 32 ? 32 : TOK;
     static constexpr uint32_t kOffW = 0;
     static constexpr uint32_t kOffT = kOffW + STAGES * kWBytes;
-    static constexpr uint32_t kOffRecv = kOffT + STAGES * kTBytes;  // [S slots][128/S rows][TOK] fp32 = 128*TOK*4
-    static constexpr uint32_t kOffBar = kOffRecv + kBM * TOK * 4;
+    static constexpr uint32_t kOffBar = kOffT + STAGES * kTBytes;
     static constexpr uint32_t kNumBars = 2 * STAGES + 1;
     static constexpr uint32_t kOffMisc = kOffBar + kNumBars * 8;
-    static constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;
+    static constexpr uint32_t kOffRecv = (kOffMisc + 16 + 15) & ~15u;   // [TOK/4][S slots x 128/S rows][4] fp32, S > 1 only
+    static constexpr uint32_t kRecvBytes = kBM * TOK * 4;
+    static constexpr uint32_t kSmemNoRecv = kOffRecv + 1024;
+    static constexpr uint32_t kSmemBytes = kSmemNoRecv + kRecvBytes;
+    static constexpr uint32_t kTwoPerSm = 115712;                   // (228 KiB - 2 x 1 KiB reserved) / 2
     static_assert(kSmemBytes <= 232448, "exceeds 227 KiB of shared memory");
     static_assert(TOK == 16 || TOK == 32 || TOK == 64, "token tile");
 };
@@ -1546,10 +1553,11 @@ hgemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_con
         const uint32_t recv_local = smem_base + C::kOffRecv;
         if (S > 1 && owner != rank) {
             // my partial sums for a row another CTA owns: slot `rank` of the owner's receive buffer
-            const uint32_t dst = mapa(recv_local + ((rank * rows_per + (row - owner * rows_per)) * TOK) * 4u, owner);
+            // layout [TOK/4][S slots x rows][4]: the 32 rows of a warp are 32 consecutive 16-byte words (no bank conflicts)
+            const uint32_t dst = mapa(recv_local + (rank * rows_per + (row - owner * rows_per)) * 16u, owner);
 #pragma unroll
             for (uint32_t j = 0; j < TOK / 4; ++j)
-                st_cluster_v4(dst + 16u * j, f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
+                st_cluster_v4(dst + j * (kBM * 16u), f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
         }
         if (S > 1) {
             __syncwarp();
@@ -1561,10 +1569,10 @@ hgemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_con
             const float *recv = reinterpret_cast<const float *>(smem_gen + C::kOffRecv);
             for (uint32_t r2 = 0; r2 < S; ++r2) {
                 if (r2 == rank) continue;
-                const float4 *src = reinterpret_cast<const float4 *>(recv + (r2 * rows_per + (row - rank * rows_per)) * TOK);
+                const float4 *src = reinterpret_cast<const float4 *>(recv) + (r2 * rows_per + (row - rank * rows_per));
 #pragma unroll
                 for (uint32_t j = 0; j < TOK / 4; ++j) {
-                    const float4 v = src[j];
+                    const float4 v = src[j * kBM];
                     f[4 * j] += v.x; f[4 * j + 1] += v.y; f[4 * j + 2] += v.z; f[4 * j + 3] += v.w;
                 }
             }
@@ -2038,7 +2046,7 @@ cudaError_t launch_skinny(const GemmArgs &g, const DeviceInfo &d, int split, cud
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(tiles * split), 1, 1);
     cfg.blockDim = dim3(kThreads, 1, 1);
-    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cfg.dynamicSmemBytes = split == 1 ? C::kSmemNoRecv : C::kSmemBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     cfg.attrs = attr;
@@ -2049,13 +2057,34 @@ cudaError_t launch_skinny(const GemmArgs &g, const DeviceInfo &d, int split, cud
 }
 
 // Cluster size for the skinny kernel: the largest S in {1,2,4,8} that keeps tiles * S within ~1.1 waves
-// of the SMs and leaves every k-slice at least four k-blocks.
-int choose_skinny_split(const GemmArgs &g, int sm_count) {
+// of the CTA slots (SMs, or twice that for the configurations of which two fit on an SM) and leaves every
+// k-slice at least four k-blocks.
+int choose_skinny_split(const GemmArgs &g, int slots) {
     const int64_t tiles = (g.n + 127) / 128, k_blocks = (g.k + 63) / 64;
     int best = 1;
     for (int s = 2; s <= 8; s *= 2)
-        if (tiles * s * 10 <= static_cast<int64_t>(sm_count) * 11 && k_blocks >= 4 * s) best = s;
+        if (tiles * s * 10 <= static_cast<int64_t>(slots) * 11 && k_blocks >= 4 * s) best = s;
     return best;
+}
+
+// Skinny kernel: which instantiation.  Up to 16 tokens: always two CTAs per SM (5 stages of 18 KiB with the
+// receive buffer, 6 without).  17-32 tokens: two per SM (5 x 20 KiB, no receive buffer) once there are more
+// tiles than SMs, where one CTA per SM would run in waves; the deep single-CTA pipelines (10 x 20 KiB,
+// 8 x 24 KiB) otherwise and for 33-64 tokens.  Measured, us (one per SM -> two per SM; cuBLAS): 16 x 4096 x
+// 4096 12.7 -> 11.1 (15.2), 16 x 14336 x 4096 24.0 -> 22.2 (23.8), 16 x 128256 x 4096 171.6 -> 158.3 (158.2),
+// 8 x 8192 x 8192 27.0 -> 23.8 (25.7), 32 x 128256 x 4096 177.1 -> 161.9 (164.7).  Not taken: 32 x 4096 x 4096
+// with two per SM and a cluster of 8 (12.0 -> 13.0), 64 x 128256 x 4096 with two per SM and 4 stages of
+// 24 KiB (184.2 -> 198.4).
+template <bool BF16>
+cudaError_t launch_skinny_any(const GemmArgs &g, const DeviceInfo &d, int sms, int forced_split, cudaStream_t stream) {
+    const int64_t tiles = (g.n + 127) / 128;
+    const bool two = g.m <= 16 || (g.m <= 32 && tiles > sms);
+    int sp = choose_skinny_split(g, two ? 2 * sms : sms);
+    if (forced_split > 0) sp = forced_split;
+    if (g.m <= 16) return sp == 1 ? launch_skinny<16, 6, BF16>(g, d, sp, stream) : launch_skinny<16, 5, BF16>(g, d, sp, stream);
+    if (g.m <= 32) return two && sp == 1 ? launch_skinny<32, 5, BF16>(g, d, sp, stream)
+                                         : launch_skinny<32, 10, BF16>(g, d, sp, stream);
+    return launch_skinny<64, 8, BF16>(g, d, sp, stream);
 }
 
 template <int CTA_GROUP, int BN, int STAGES, int MT = 1>
@@ -2200,23 +2229,9 @@ int hgemm_launch(const GemmArgs &g, int variant, int block_n, int max_sms, cudaS
     static const bool env_no_skinny = tune_env_int("PEAKGEMM_TUNE_SKINNY", 1) == 0;
     if (variant == 4 || (variant == 0 && g.m <= 64 && !env_no_skinny)) {
         if (g.m > 64) return kLaunchBadConfig;
-        static const int env_two = tune_env_int("PEAKGEMM_TUNE_SKINNY_TWO", 0);
-        int sp = choose_skinny_split(g, env_two ? 2 * sms : sms);
-        if (variant == 4 && env_split >= 1 && env_split <= 8 && (env_split & (env_split - 1)) == 0) sp = env_split;
-        if (env_two) {
-            if (g.m <= 16) e = g.bf16 ? launch_skinny<16, 5, true>(g, *d, sp, stream)
-                                      : launch_skinny<16, 5, false>(g, *d, sp, stream);
-            else if (g.m <= 32) e = g.bf16 ? launch_skinny<32, 4, true>(g, *d, sp, stream)
-                                           : launch_skinny<32, 4, false>(g, *d, sp, stream);
-            else e = g.bf16 ? launch_skinny<64, 3, true>(g, *d, sp, stream)
-                            : launch_skinny<64, 3, false>(g, *d, sp, stream);
-        } else
-        if (g.m <= 16) e = g.bf16 ? launch_skinny<16, 12, true>(g, *d, sp, stream)
-                                  : launch_skinny<16, 12, false>(g, *d, sp, stream);
-        else if (g.m <= 32) e = g.bf16 ? launch_skinny<32, 10, true>(g, *d, sp, stream)
-                                       : launch_skinny<32, 10, false>(g, *d, sp, stream);
-        else e = g.bf16 ? launch_skinny<64, 8, true>(g, *d, sp, stream)
-                        : launch_skinny<64, 8, false>(g, *d, sp, stream);
+        int forced = 0;
+        if (variant == 4 && env_split >= 1 && env_split <= 8 && (env_split & (env_split - 1)) == 0) forced = env_split;
+        e = g.bf16 ? launch_skinny_any<true>(g, *d, sms, forced, stream) : launch_skinny_any<false>(g, *d, sms, forced, stream);
         if (e != cudaSuccess) { *cuda_err = e; return kLaunchCuda; }
         return kLaunchOk;
     }

@@ -174,19 +174,24 @@ def test_split_k_is_deterministic_and_refuses_unsplittable_shapes(cuda):
 
 
 # ---- skinny kernel (variant 4, m <= 64): operands swapped, optional cluster split-K over k.
-# n = 128 * tiles steers the cluster size: 16 tiles -> S=8, 32 -> 4, 64 -> 2, >= 128 -> 1.
+# n = 128 * tiles steers the cluster size.  Up to 16 tokens (two CTAs per SM, 296 slots): 16 and 32 tiles -> S=8,
+# 64 -> 4, 112 -> 2, >= 163 -> 1.  17-64 tokens: 16 tiles -> S=8, 32 -> 4, 64 -> 2, >= 128 -> 1 with one CTA per SM and
+# the deep pipeline; 17-32 tokens and more than 148 tiles: two CTAs per SM, short pipeline, no receive buffer.
 @pytest.mark.parametrize("dtype", [BF16, F16])
 @pytest.mark.parametrize("m,n,k", [
     (16, 2048, 2048),      # S=8, 16 rows per CTA
     (1, 2048, 4096),       # a single token
-    (16, 4096, 4096),      # S=4 (benchmark config 3)
+    (16, 4096, 4096),      # S=8 (benchmark config 3)
     (17, 4096, 1024),      # 32-token tile, S=4
     (33, 8192, 512),       # 64-token tile, S=2
     (64, 8192, 4096),      # full 64-token tile
-    (16, 14336, 4096),     # S=1, 112 CTAs
+    (16, 14336, 4096),     # S=2, 224 CTAs on 148 SMs
     (7, 1000, 264),        # tails in n and k, too few k-blocks to split
     (16, 128, 64),         # one CTA, one k-block
-    (48, 16384 + 8, 192),  # more CTAs than SMs, ragged last tile
+    (48, 16384 + 8, 192),  # 129 CTAs of the deep 64-token pipeline, ragged last tile
+    (12, 21000, 1024),     # 16-token tile, S=1, no receive buffer: 165 CTAs, two per SM, the ring wraps twice
+    (24, 19208, 448),      # 32-token tile, two CTAs per SM (151 tiles), ragged last tile, ring wraps
+    (48, 20000, 704),      # 64-token tile, 157 CTAs on 148 SMs
 ])
 def test_skinny_kernel(cuda, m, n, k, dtype):
     run_case(m, n, k, dtype, 4, 0, seed=8, gen=oracle.gemm_inputs_llm)
