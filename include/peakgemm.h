@@ -86,8 +86,10 @@ int pg_hgemm(void *c, const void *a, const void *b,
  *               combined through distributed shared memory, no global scratch.
  *               PG_ERR_BAD_ARG if the shape admits no split (k < 256, or too many tiles)
  *   variant 4 = skinny kernel for m <= 64 (weight streaming): the weights take the
- *               128-row side of the MMA, the tokens its 16/32/64-wide side, 8-12 TMA
- *               stages deep, optional cluster split-K as in variant 3; block_n ignored.
+ *               128-row side of the MMA, the tokens its 16/32/64-wide side, 8-10 TMA
+ *               stages deep (or two resident CTAs per SM of 5-6 stages each: up to 16 tokens,
+ *               and 17-32 tokens with more tiles than SMs), optional cluster split-K as in
+ *               variant 3; block_n ignored.
  *               PG_ERR_BAD_ARG if m > 64
  *   variant 5 = CTA pair per 512 x 256 tile: two 256-row blocks share every k-block of B
  *               and their two accumulators fill tensor memory (25 % fewer operand bytes
