@@ -2074,13 +2074,21 @@ int choose_skinny_split(const GemmArgs &g, int slots) {
 // 4096 12.7 -> 11.1 (15.2), 16 x 14336 x 4096 24.0 -> 22.2 (23.8), 16 x 128256 x 4096 171.6 -> 158.3 (158.2),
 // 8 x 8192 x 8192 27.0 -> 23.8 (25.7), 32 x 128256 x 4096 177.1 -> 161.9 (164.7).  Not taken: 32 x 4096 x 4096
 // with two per SM and a cluster of 8 (12.0 -> 13.0), 64 x 128256 x 4096 with two per SM and 4 stages of
-// 24 KiB (184.2 -> 198.4).
+// 24 KiB (184.2 -> 198.4).  17-32 tokens with one wave of tiles that one CTA per SM leaves unsplit (82-162 tiles):
+// two per SM with 4 x 20 KiB and k split in two, 32 x 14336 x 4096 24.0 -> 22.9 (23.4), 32 x 11008 x 4096
+// 22.1 -> 19.5 (20.5), 32 x 14336 x 8192 40.6 -> 41.3 (39.4).
 template <bool BF16>
 cudaError_t launch_skinny_any(const GemmArgs &g, const DeviceInfo &d, int sms, int forced_split, cudaStream_t stream) {
     const int64_t tiles = (g.n + 127) / 128;
     const bool two = g.m <= 16 || (g.m <= 32 && tiles > sms);
     int sp = choose_skinny_split(g, two ? 2 * sms : sms);
     if (forced_split > 0) sp = forced_split;
+    // 17-32 tokens, one wave of tiles that one CTA per SM cannot split over k (more than 0.55 x SMs tiles): two CTAs
+    // per SM, each half of k
+    static const bool env_two32 = tune_env_int("PEAKGEMM_TUNE_SKINNY_TWO32", 1) != 0;
+    if (env_two32 && forced_split <= 0 && !two && g.m > 16 && g.m <= 32 && sp == 1 && tiles * 20 <= sms * 22 &&
+        (g.k + 63) / 64 >= 8)
+        return launch_skinny<32, 4, BF16>(g, d, 2, stream);
     if (g.m <= 16) return sp == 1 ? launch_skinny<16, 6, BF16>(g, d, sp, stream) : launch_skinny<16, 5, BF16>(g, d, sp, stream);
     if (g.m <= 32) return two && sp == 1 ? launch_skinny<32, 5, BF16>(g, d, sp, stream)
                                          : launch_skinny<32, 10, BF16>(g, d, sp, stream);

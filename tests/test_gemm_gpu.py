@@ -176,7 +176,8 @@ def test_split_k_is_deterministic_and_refuses_unsplittable_shapes(cuda):
 # ---- skinny kernel (variant 4, m <= 64): operands swapped, optional cluster split-K over k.
 # n = 128 * tiles steers the cluster size.  Up to 16 tokens (two CTAs per SM, 296 slots): 16 and 32 tiles -> S=8,
 # 64 -> 4, 112 -> 2, >= 163 -> 1.  17-64 tokens: 16 tiles -> S=8, 32 -> 4, 64 -> 2, >= 128 -> 1 with one CTA per SM and
-# the deep pipeline; 17-32 tokens and more than 148 tiles: two CTAs per SM, short pipeline, no receive buffer.
+# the deep pipeline; 17-32 tokens and more than 148 tiles: two CTAs per SM, short pipeline, no receive buffer; 17-32
+# tokens and 82-162 tiles: two CTAs per SM with S=2.
 @pytest.mark.parametrize("dtype", [BF16, F16])
 @pytest.mark.parametrize("m,n,k", [
     (16, 2048, 2048),      # S=8, 16 rows per CTA
@@ -192,6 +193,7 @@ def test_split_k_is_deterministic_and_refuses_unsplittable_shapes(cuda):
     (12, 21000, 1024),     # 16-token tile, S=1, no receive buffer: 165 CTAs, two per SM, the ring wraps twice
     (24, 19208, 448),      # 32-token tile, two CTAs per SM (151 tiles), ragged last tile, ring wraps
     (48, 20000, 704),      # 64-token tile, 157 CTAs on 148 SMs
+    (24, 14336, 1024),     # 32-token tile, one wave of 112 tiles: two CTAs per SM, k split in two, ring of 4 wraps
 ])
 def test_skinny_kernel(cuda, m, n, k, dtype):
     run_case(m, n, k, dtype, 4, 0, seed=8, gen=oracle.gemm_inputs_llm)
