@@ -639,6 +639,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
             bool ok = true;
             const uint64_t pol_store = l2_policy_evict_first();
             const bool fused = epi.any();
+            const bool wide_boxes = n_dst > 1 || epi.mc_dst != nullptr;      // the launcher encodes 64-column boxes then
             for (uint32_t it = 0; ok; ++it) {
                 const Unit u = unit_at(it, worker, workers, total_tiles, k_blocks, tail);
                 if (!u.valid) break;
@@ -665,6 +666,44 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                     if (lane == 0) mbar_arrive_cluster(acc_empty_leader + mt * 8);
                     const bool row_ok = row0 + lane < M;
                     const float rs = fused ? epi_row_scale(epi, row_ok, row0 + lane) : 1.f;
+                    if (wide_boxes) {
+                        // Stores that cross NVLink (peer destinations, or a multicast one): two 32 x 64 boxes with
+                        // 128-byte rows over the warp's whole staging area, one at a time.  Half as many, twice as
+                        // long writes arrive at every peer as with the 64-byte rows of the 32 x 32 boxes.
+#pragma unroll
+                        for (uint32_t cp = 0; cp < 2; ++cp) {
+                            const uint32_t col0 = ni * BN + half * 128u + cp * 64u;
+                            uint4 o[8];
+#pragma unroll
+                            for (uint32_t c = 0; c < 8; ++c) {
+                                const uint32_t *src = &v[2u * cp + (c >> 2)][(c & 3u) * 8u];
+                                o[c].x = pack2<BF16>(__uint_as_float(src[0]), __uint_as_float(src[1]));
+                                o[c].y = pack2<BF16>(__uint_as_float(src[2]), __uint_as_float(src[3]));
+                                o[c].z = pack2<BF16>(__uint_as_float(src[4]), __uint_as_float(src[5]));
+                                o[c].w = pack2<BF16>(__uint_as_float(src[6]), __uint_as_float(src[7]));
+                            }
+                            // the previous store from this area must have finished reading it
+                            if (lane == 0) bulk_wait_group_read<0>();
+                            __syncwarp();
+                            // row `lane` = 128 bytes, chunk c at position c ^ (row % 8)  (128-byte swizzle)
+#pragma unroll
+                            for (uint32_t c = 0; c < 8; ++c)
+                                *reinterpret_cast<uint4 *>(sbuf_gen + lane * 128u + ((c ^ (lane & 7u)) << 4)) = o[c];
+                            fence_proxy_async_smem();
+                            __syncwarp();
+                            if (epi.mc_dst != nullptr) {
+                                mc_store_box<64>(sbuf_gen, epi.mc_dst, epi.ld_mc, row0, col0, M, N, lane);
+                            } else if (lane == 0) {
+                                if (row0 < M && col0 < N) {
+                                    for (uint32_t d = 0; d < n_dst; ++d)
+                                        tma_store_2d(&tm_c.m[d], sbuf, static_cast<int32_t>(col0),
+                                                     static_cast<int32_t>(row0));
+                                }
+                                bulk_commit_group();
+                            }
+                        }
+                        continue;
+                    }
 #pragma unroll
                     for (uint32_t cb = 0; cb < 4; ++cb) {       // four 32 x 32 boxes, two staging buffers in turn
                         const uint32_t col0 = ni * BN + half * 128u + cb * 32u;
@@ -1839,12 +1878,14 @@ cudaError_t launch(const GemmArgs &g, const DeviceInfo &d, int sms, cudaStream_t
     }
     CUtensorMap tm_a, tm_b;
     DstMaps tm_c = {};
+    // several destinations (or a multicast one): every store box is 64 columns wide, 128-byte rows (see the kernel)
+    const uint32_t store_box_cols = (g.n_extra_dst > 0 || g.mc_dst) ? kStoreCols : C::kStoreBoxCols;
     if (!make_tmap(&tm_a, g.a, g.m, g.k, g.lda, kBM, BF16, false) ||
         !make_tmap(&tm_b, g.b, g.n, g.k, g.ldb, C::kBRows, BF16, false) ||
-        !make_tmap(&tm_c.m[0], g.c, g.m, g.n, g.ldc, kStoreRows, BF16, true, C::kStoreBoxCols))
+        !make_tmap(&tm_c.m[0], g.c, g.m, g.n, g.ldc, kStoreRows, BF16, true, store_box_cols))
         return cudaErrorInvalidValue;
     for (int i = 0; i < g.n_extra_dst; ++i)
-        if (!make_tmap(&tm_c.m[1 + i], g.extra_dst[i], g.m, g.n, g.ldc, kStoreRows, BF16, true, C::kStoreBoxCols))
+        if (!make_tmap(&tm_c.m[1 + i], g.extra_dst[i], g.m, g.n, g.ldc, kStoreRows, BF16, true, store_box_cols))
             return cudaErrorInvalidValue;
     const uint32_t n_dst = 1u + static_cast<uint32_t>(g.n_extra_dst);
 
