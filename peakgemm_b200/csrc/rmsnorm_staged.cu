@@ -423,6 +423,11 @@ Plan make_plan(int64_t h, bool bwd) {
     int T = static_cast<int>((h8 / per_thread + 31) / 32 * 32);
     if (T < 32) T = 32;
     if (T > 256) T = 256;
+    // Forward, 4096 < h < 8192: groups of 256 would own 3-4 vectors per thread with up to a quarter of the slots
+    // empty and leave 3 rows in flight per CTA; groups of 128 (5-7 vectors, 6 groups) measured 6072 against 4749 GB/s
+    // at h = 5120, 5997 against 5460 at 6144, 5751 against 5373 at 7168 ([32768, h] bf16).  At h = 4096 and 8192 the
+    // groups of 256 are faster (6298 against 5869, 5927 against 5724).
+    if (!bwd && h8 > 512 && h8 < 1024) T = 128;
     // Benchmark override (builds with PG_ENABLE_TUNING only), read once: PEAKGEMM_TUNE_RMS_T = threads per
     // consumer group (32..256).
     static const int env_t = tune_env_int("PEAKGEMM_TUNE_RMS_T", 0);

@@ -54,7 +54,8 @@ def run_bwd(rows, h, dtype, seed=3, eps=1e-6):
 
 @pytest.mark.parametrize("dtype", [BF16, F16])
 @pytest.mark.parametrize("rows,h", [(1, 8), (7, 64), (33, 256), (100, 1000), (257, 4096), (64, 8192),
-                                    (19, 5120), (5, 16384), (3, 24576), (1, 2048), (301, 2048), (1000, 3072)])
+                                    (19, 5120), (5, 16384), (3, 24576), (1, 2048), (301, 2048), (1000, 3072),
+                                    (2000, 5120), (700, 6144), (900, 7168), (600, 7176)])
 def test_fwd_shapes(cuda, rows, h, dtype):
     run_fwd(rows, h, dtype)
 
