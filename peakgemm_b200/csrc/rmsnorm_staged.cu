@@ -437,7 +437,22 @@ Plan make_plan(int64_t h, bool bwd) {
     p.T = T;
     p.G = (bwd ? Threads<true, 1>::kConsumers : p.vpt >= 4 ? Threads<false, 4>::kConsumers : Threads<false, 1>::kConsumers) / T;
     if (p.G > 8) p.G = 8;
-    for (int s = kMaxStages; s >= 2; --s) {
+    // Ring depth.  More rows in flight are not always better in the forward pass: with groups of 256 threads (three
+    // groups) about 64 KiB of rows in flight per SM measured best on [32768, h] bf16 — h = 4096: 9 slots 6500 GB/s
+    // against 6324 with 15; h = 8192: 3 slots (one per group, refilled as soon as the group has the row in registers)
+    // 6144 against 6009 with 12; h = 12288: 3 slots 6107 against 5965 with 6.  The backward pass and the narrower
+    // groups keep the deepest ring that fits (h = 8192 backward: 6604 with 6 slots, 6361 with 3).
+    // PEAKGEMM_TUNE_RMS_STAGES (builds with PG_ENABLE_TUNING only) caps the depth instead.
+    int max_stages = kMaxStages;
+    if (!bwd && T == 256) {
+        const int64_t per_round = 3 * h * 2;                      // one row of 16-bit elements per group
+        int rounds = static_cast<int>((65536 + per_round / 2) / per_round);
+        if (rounds < 1) rounds = 1;
+        max_stages = 3 * rounds < kMaxStages ? 3 * rounds : kMaxStages;
+    }
+    static const int env_stages = tune_env_int("PEAKGEMM_TUNE_RMS_STAGES", 0);
+    if (env_stages >= 2 && env_stages <= kMaxStages) max_stages = env_stages;
+    for (int s = max_stages; s >= 2; --s) {
         const Layout l = make_layout(static_cast<int>(h), bwd, s);
         if (l.total > kSmemBudget) continue;
         // The ring depth must be a multiple of the number of groups, so that a slot is always consumed by the SAME
