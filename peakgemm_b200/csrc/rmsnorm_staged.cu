@@ -42,7 +42,9 @@ namespace {
 // its gamma values in registers; backward: 512 (its dgamma shares and both operands need ~96 registers per thread).
 template <bool BWD, int VPT>
 struct Threads {
-    static constexpr int kConsumers = BWD ? 512 : (VPT >= 4 ? 768 : 960);     // + 32 <= 1024 threads per CTA
+    // Backward with 8 vectors per thread (h > 8192): 64 dgamma sums, both operands and the output of a row need about
+    // 160 registers; at 544 threads the compiler has 96 and spills (3.3-3.6 TB/s).  One group of 256 instead.
+    static constexpr int kConsumers = BWD ? (VPT == 8 ? 256 : 512) : (VPT >= 4 ? 768 : 960);   // + 32 <= 1024 threads per CTA
     static constexpr int kTotal = kConsumers + 32;
 };
 template <bool BWD> struct RowIndex { using type = int64_t; };
@@ -435,7 +437,7 @@ Plan make_plan(int64_t h, bool bwd) {
     const int need = static_cast<int>((h8 + T - 1) / T);
     p.vpt = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
     p.T = T;
-    p.G = (bwd ? Threads<true, 1>::kConsumers : p.vpt >= 4 ? Threads<false, 4>::kConsumers : Threads<false, 1>::kConsumers) / T;
+    p.G = (bwd ? (p.vpt == 8 ? Threads<true, 8>::kConsumers : Threads<true, 1>::kConsumers) : p.vpt >= 4 ? Threads<false, 4>::kConsumers : Threads<false, 1>::kConsumers) / T;
     if (p.G > 8) p.G = 8;
     // Ring depth.  More rows in flight are not always better in the forward pass: with groups of 256 threads (three
     // groups) about 64 KiB of rows in flight per SM measured best on [32768, h] bf16 — h = 4096: 9 slots 6500 GB/s
